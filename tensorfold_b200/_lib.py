@@ -1,0 +1,96 @@
+"""ctypes binding of ``libtensorfold_b200.so`` (the C ABI in ``include/tensorfold_b200.h``).
+
+There is no fallback: if the library is missing, importing a kernel wrapper raises. Tensors cross
+the boundary as raw device pointers; the stream is torch's current stream.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_size_t, c_void_p, c_float, c_longlong
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libtensorfold_b200.so"
+
+TF_OK, TF_EINVAL, TF_EALIGN, TF_ESCRATCH, TF_ECUDA, TF_ESTALL = 0, -1, -2, -3, -4, -5
+_NAMES = {TF_EINVAL: "TF_EINVAL (unsupported shape, size or flag)", TF_EALIGN: "TF_EALIGN (misaligned pointer)",
+          TF_ESCRATCH: "TF_ESCRATCH (scratch missing or too small)", TF_ECUDA: "TF_ECUDA (launch refused)",
+          TF_ESTALL: "TF_ESTALL (a bounded device wait ran out)"}
+
+# name -> (restype, argtypes); the single list the loader, the tests and the header must agree on
+SIGNATURES: dict[str, tuple] = {
+    "tf_version": (c_int, []),
+    "tf_qmm_workers": (c_int, []),
+    "tf_qmm_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
+                       c_void_p, c_void_p]),
+    "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_qmm_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_group_sums": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """The kernel library, loaded once. Raises if it has not been built."""
+
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m tensorfold_b200.build` "
+                               "(there is no CPU or PyTorch fallback for the lane kernels)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != TF_OK:
+        err = ValueError if code in (TF_EINVAL, TF_EALIGN, TF_ESCRATCH) else RuntimeError
+        raise err(f"{what}: {_NAMES.get(code, code)}")
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("lane kernels take CUDA tensors only (there is no CPU path)")
+
+
+class Status:
+    """The device status word kernels report a run-out bounded wait to; read at sync points."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def raise_if_set(self) -> None:
+        code = int(self.word.item())
+        if code:
+            self.word.zero_()
+            raise RuntimeError(f"a lane kernel reported {_NAMES.get(code, code)}")
+
+
+_status: dict[int, Status] = {}
+
+
+def status(device) -> Status:
+    idx = torch.device(device).index or 0
+    if idx not in _status:
+        _status[idx] = Status(device)
+    return _status[idx]

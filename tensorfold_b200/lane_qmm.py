@@ -1,0 +1,196 @@
+"""Row-invariant 4-bit projections on B200: the lane matmul.
+
+Host-side mirror of the reference's ``lane_qmm`` interface (Metal:
+``kernels/qwen/dense/v1/lane_qmm.py:244-335``; CUDA: ``families/qwen3_5/cuda/qmm.py:38-144`` and
+``qmm_fast.py:80-215``; group 32: ``families/qwen4_exp/cuda/qmm.py:56-125,246-285``). Same names,
+argument meaning and errors; the arithmetic is this library's own (see ``csrc/qmm.cu``): one chain
+of tensor-core steps per output for every row count, K segments fixed by the weight's shape.
+
+Weights are MLX affine 4-bit: ``(N, K/8)`` uint32 words, element i of a row at bits ``4*(i%8)`` of
+word ``i//8``, with ``(N, K/group)`` bf16 scales and biases, group 64 or 32. ``tile_weight`` regroups
+them once into the streaming layout the kernel reads (same bits, no information lost;
+``untile_weight`` restores the stored layout).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+MAX_ROWS = 128           # rows one kernel launch accepts (reference: lane_qmm.MAX_ROWS)
+WORKERS = 148            # persistent CTAs the K schedule is cut for (a library constant, not the device's SM count)
+COLUMN_BLOCK = 128       # output columns per column block
+ITEM_TILES = 4           # 64-input k tiles per schedule item, the same for every row count
+
+
+@dataclass
+class QWeight:
+    """A 4-bit projection in the kernel's tile layout."""
+
+    tiled: torch.Tensor      # uint8, tf_qmm_tiled_bytes(n, k, group)
+    n: int
+    k: int
+    group: int
+
+    def nbytes(self) -> int:
+        return self.tiled.numel()
+
+    @property
+    def device(self):
+        return self.tiled.device
+
+
+def _check_weight(weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group: int | None):
+    if weight.dim() != 2 or weight.dtype not in (torch.int32, torch.uint32):
+        raise ValueError("lane_qmm: weight must be (N, K/8) 32-bit words")
+    n, k8 = weight.shape
+    k = k8 * 8
+    if group is None:
+        group = k // scales.shape[1]
+    if group not in (32, 64) or k % 64 or scales.shape != (n, k // group) or biases.shape != scales.shape:
+        raise ValueError(f"lane_qmm: unsupported weight {tuple(weight.shape)} with scales {tuple(scales.shape)}")
+    if scales.dtype != torch.bfloat16 or biases.dtype != torch.bfloat16:
+        raise ValueError("lane_qmm: scales and biases must be bf16")
+    return n, k, group
+
+
+def tile_weight(weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group: int | None = None) -> QWeight:
+    """Stored MLX layout -> the kernel's tile layout (one device pass; same bits, new order)."""
+
+    n, k, group = _check_weight(weight, scales, biases, group)
+    _lib.need_cuda(weight, scales, biases)
+    lib = _lib.load()
+    out = torch.empty(lib.tf_qmm_tiled_bytes(n, k, group), dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        _lib.check(lib.tf_qmm_tile(weight.contiguous().data_ptr(), scales.contiguous().data_ptr(),
+                                   biases.contiguous().data_ptr(), out.data_ptr(), n, k, group, _lib.stream()),
+                   "tile_weight")
+    return QWeight(out, n, k, group)
+
+
+def untile_weight(q: QWeight) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``tile_weight`` undone: (words int32 (N, K/8), scales, biases bf16 (N, K/group))."""
+
+    lib = _lib.load()
+    dev = q.tiled.device
+    words = torch.empty((q.n, q.k // 8), dtype=torch.int32, device=dev)
+    scales = torch.empty((q.n, q.k // q.group), dtype=torch.bfloat16, device=dev)
+    biases = torch.empty_like(scales)
+    with torch.cuda.device(dev):
+        _lib.check(lib.tf_qmm_untile(q.tiled.data_ptr(), words.data_ptr(), scales.data_ptr(), biases.data_ptr(),
+                                     q.n, q.k, q.group, _lib.stream()), "untile_weight")
+    return words, scales, biases
+
+
+def pack_scales(scales: torch.Tensor, biases: torch.Tensor) -> torch.Tensor:
+    """(N, K/g) scales and biases -> (K/g, N, 2) bf16 pairs, group-major (the reference's helper;
+    this library keeps the pairs inside the tiled weight instead)."""
+
+    return torch.stack([scales.t(), biases.t()], dim=-1).to(torch.bfloat16).contiguous()
+
+
+def segments(n: int, k: int) -> list[list[tuple[int, int]]]:
+    """The K schedule: for each 128-column block, the k-tile ranges (64 inputs a tile) whose sums are
+    formed separately and then added in order. A function of the shape and the worker count only —
+    never of the row count."""
+
+    kts = ITEM_TILES
+    kt = k // 64
+    cb = -(-(-(-n // 16)) // (COLUMN_BLOCK // 16))
+    spb = -(-kt // kts)
+    total = cb * spb
+    bounds = [i * total // WORKERS for i in range(WORKERS + 1)]
+    out: list[list[tuple[int, int]]] = [[] for _ in range(cb)]
+    for i in range(WORKERS):
+        it = bounds[i]
+        while it < bounds[i + 1]:
+            c = it // spb
+            end = min((c + 1) * spb, bounds[i + 1])
+            out[c].append(((it - c * spb) * kts, min(kt, (end - c * spb) * kts)))
+            it = end
+    return out
+
+
+def split_k(n: int, k: int) -> int:
+    """K segments an (n, k) weight's columns are summed in (the most any column block gets):
+    fixed by the shape, never by the row count (reference: ``lane_qmm.split_k``)."""
+
+    return max(len(s) for s in segments(n, k))
+
+
+def group_sums(x: torch.Tensor, group: int = 64) -> torch.Tensor:
+    """(M, K) bf16 -> (M, K/group) fp32 sums of each input group (reference: ``qmm.group_sums``)."""
+
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("group_sums: x must be a 2-D bf16 tensor")
+    _lib.need_cuda(x)
+    m, k = x.shape
+    x = x.contiguous()
+    xs = torch.empty((m, k // group), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().tf_group_sums(x.data_ptr(), xs.data_ptr(), m, k, group, _lib.stream()), "group_sums")
+    return xs
+
+
+_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def scratch_for(device: torch.device) -> torch.Tensor:
+    """Per (device, stream) matmul scratch: zeroed counters + parked partial blocks."""
+
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None:
+        size = _lib.load().tf_qmm_scratch_bytes(MAX_ROWS, 1, 64, 64)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def lane_matmul(x: torch.Tensor, weight: QWeight, xs: torch.Tensor | None = None, *, f32: bool = False,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """x (..., K) bf16 times the 4-bit ``weight`` (N, K) transposed -> (..., N) bf16.
+
+    ``xs``: x's group sums when the producing kernel already wrote them. ``f32``: return the
+    unrounded fp32 sums (a tensor-parallel rank's partial). More than ``MAX_ROWS`` rows run as
+    several launches; a row's bits do not depend on which launch it rides in.
+    """
+
+    if x.dtype != torch.bfloat16:
+        raise ValueError("lane_matmul: x must be bf16")
+    if x.shape[-1] != weight.k:
+        raise ValueError(f"lane_matmul: weight (N={weight.n}, K={weight.k}) does not match K={x.shape[-1]}")
+    _lib.need_cuda(x)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, weight.k).contiguous()
+    m = x2.shape[0]
+    if m < 1:
+        raise ValueError("lane_matmul: needs at least one row")
+    if xs is None:
+        xs = group_sums(x2, weight.group)
+    xs = xs.reshape(m, weight.k // weight.group)
+    if xs.dtype != torch.float32 or not xs.is_contiguous():
+        raise ValueError("lane_matmul: xs must be contiguous fp32 (M, K/group)")
+    dtype = torch.float32 if f32 else torch.bfloat16
+    if out is None:
+        out = torch.empty((m, weight.n), dtype=dtype, device=x.device)
+    elif out.shape != (m, weight.n) or out.dtype != dtype or not out.is_contiguous():
+        raise ValueError("lane_matmul: out has the wrong shape or dtype")
+    lib = _lib.load()
+    scratch = scratch_for(x.device)
+    st = _lib.status(x.device)
+    with torch.cuda.device(x.device):
+        for r0 in range(0, m, MAX_ROWS):
+            r1 = min(m, r0 + MAX_ROWS)
+            _lib.check(lib.tf_qmm(x2[r0:r1].data_ptr(), xs[r0:r1].data_ptr(), weight.tiled.data_ptr(),
+                                  out[r0:r1].data_ptr(), scratch.data_ptr(), scratch.numel(), r1 - r0, weight.n,
+                                  weight.k, weight.group, 1 if f32 else 0, st.word.data_ptr(), _lib.stream()),
+                       "lane_matmul")
+    return out.reshape(*lead, weight.n)
+
+
+__all__ = ["MAX_ROWS", "QWeight", "group_sums", "lane_matmul", "pack_scales", "segments", "split_k", "tile_weight",
+           "untile_weight"]
