@@ -48,18 +48,27 @@ int tf_qmm_workers(void);
  *   y[m, n] = round_bf16( sum over groups g in order of  s[n,g] * (x[m, g-block] . q[n, g-block])
  *                                                       + b[n,g] * xs[m,g] )
  *
- * x  [M, K] bf16 row-major, M in 1..128.   xs [M, K/group] fp32: sum of each group's inputs.
- * w_tiled: weights in this library's tile layout (tf_qmm_tiled_bytes / tf_qmm_tile_* below).
+ * x_packed: the M input rows (1..128) in packed form — per 64-input k tile, Mp = M rounded up to 4
+ *          rows of 128 bytes, then the tile's group sums [64/group][Mp] fp32; tf_packed_bytes bytes,
+ *          16-byte aligned. tf_pack_rows builds it from row-major bf16; the glue kernels below
+ *          write it directly.
+ * w_tiled: weights in this library's tile layout (tf_qmm_tiled_bytes / tf_qmm_tile below).
  * y  [M, N] bf16 (fp32 with TF_QMM_F32_OUT).  group is 64 or 32.  K a multiple of 64.
- * scratch: tf_qmm_scratch_bytes(M, N, K, group) bytes, 256-byte aligned; its first
- *          TF_QMM_COUNTER_BYTES bytes must be zero before the first call and are left zero by
- *          every call (the rest needs no initialisation). Calls that overlap on the GPU must not
- *          share scratch.
+ * scratch: tf_qmm_scratch_bytes() bytes, 256-byte aligned; its first TF_QMM_COUNTER_BYTES bytes
+ *          must be zero before the first call and are left zero by every call (the rest needs no
+ *          initialisation). Calls that overlap on the GPU must not share scratch.
  */
 #define TF_QMM_COUNTER_BYTES 16384
-size_t tf_qmm_scratch_bytes(int M, int N, int K, int group);
-int tf_qmm(const void* x, const void* xs, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes,
-           int M, int N, int K, int group, int flags, int* status, void* stream);
+size_t tf_qmm_scratch_bytes(void);
+size_t tf_packed_bytes(int M, int K, int group);
+int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
+           int K, int group, int flags, int* status, void* stream);
+
+/* Row-major bf16 rows x [M, K] -> packed rows with their group sums; when xs is not NULL the sums
+ * are also written as [M, K/group] fp32. A group's sum is formed in eights: eight (group 64) or four
+ * (group 32) sequential 8-element sums combined by a pairwise tree.
+ * Replaces: families/qwen3_5/cuda/qmm.py:49-59,106-114 (group_sums); lane_qmm.py:50-58 (xsum). */
+int tf_pack_rows(const void* x, void* x_packed, void* xs, int M, int K, int group, void* stream);
 
 /* Size in bytes of the tiled form of an [N, K] 4-bit weight with the given group size. */
 size_t tf_qmm_tiled_bytes(int N, int K, int group);
@@ -73,11 +82,6 @@ int tf_qmm_tile(const void* words, const void* scales, const void* biases, void*
                 void* stream);
 int tf_qmm_untile(const void* w_tiled, void* words, void* scales, void* biases, int N, int K, int group,
                   void* stream);
-
-/* xs[m, g] = fp32 sum of x[m, g*group : (g+1)*group], added in sixteens: four (group 64) or two
- * (group 32) sequential 16-element sums combined pairwise.
- * Replaces: families/qwen3_5/cuda/qmm.py:49-59,106-114 (group_sums); lane_qmm.py:50-58 (xsum). */
-int tf_group_sums(const void* x, void* xs, int M, int K, int group, void* stream);
 
 #ifdef __cplusplus
 }

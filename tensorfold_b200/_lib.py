@@ -24,13 +24,14 @@ _NAMES = {TF_EINVAL: "TF_EINVAL (unsupported shape, size or flag)", TF_EALIGN: "
 SIGNATURES: dict[str, tuple] = {
     "tf_version": (c_int, []),
     "tf_qmm_workers": (c_int, []),
-    "tf_qmm_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
-    "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
+    "tf_qmm_scratch_bytes": (c_size_t, []),
+    "tf_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p]),
+    "tf_pack_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
-    "tf_group_sums": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
 }
 
 _lib = None

@@ -33,6 +33,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return a | (b << 16);
 }
 
+// ---- packed activations -------------------------------------------------------------------------
+// The lane matmul reads its input rows "packed": per k tile (64 inputs), Mp = M rounded up to its row
+// bucket (8, 16, 32, 64 or 128) rows of 128 bytes each (16-byte chunk c of row r stored at chunk
+// c ^ 4*(r&1); rows past M are zero), followed by the tile's group sums as [groups in the tile][Mp] fp32. Every kernel that produces matmul input writes this
+// form directly with the two helpers below, so the sums are formed the same way everywhere.
+__host__ __device__ constexpr int tf_padded_rows(int m) { return m <= 8 ? 8 : m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
+// fp32 sum of a G-input group: each lane adds its 8 contiguous bf16 values in order, then the G/8
+// lanes holding the group combine in a pairwise tree. Call with whole warps; every lane of the
+// group gets the sum.
+template <int G>
+__device__ __forceinline__ float group_sum8(uint4 v) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { s += bf16_lo(u[i]); s += bf16_hi(u[i]); }
+#pragma unroll
+    for (int o = 1; o < G / 8; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return s;
+}
+
+// Store chunk c (inputs 8c..8c+7) of `row` and, from the group's first lane, the group's sum.
+template <int G>
+__device__ __forceinline__ void packed_store(uint8_t* xp, int Mp, int row, int c, uint4 v, float sum) {
+    constexpr int GPT = 64 / G;
+    uint8_t* tile = xp + (size_t)(c >> 3) * Mp * (128 + 4 * GPT);
+    *reinterpret_cast<uint4*>(tile + row * 128 + (((c & 7) * 16) ^ ((row & 1) << 6))) = v;
+    if ((c & (G / 8 - 1)) == 0) reinterpret_cast<float*>(tile + Mp * 128)[((c / (G / 8)) % GPT) * Mp + row] = sum;
+}
+
 // ---- shared memory / mbarrier / bulk copy (TMA, untiled) --------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -100,7 +130,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // ---- tensor-core step: D(16x8, fp32) = A(16x16, bf16) * B(16x8, bf16) + C ----------------------
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                                const float (&c)[4]) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%11,%12,%13};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])

@@ -7,19 +7,29 @@
 //       P   = tensor-core chain over the group's 16-wide k-steps of  x[m,k] * (q[n,k] + 128),
 //             started from  -128 * xs[m,g]            (so P = x . q up to fp32 rounding)
 //       acc = fma(b[n,g], xs[m,g], fma(s[n,g], P, acc))
-//   segments of K (fixed by N, K, group and the worker count only) are added in k order,
+//   segments of K (fixed by N, K and the worker count only) are added in k order,
 //   then one rounding to bf16.
 // The chain never looks at the row count, so row m of an M-row call has the bits of a 1-row call.
 //
-// Tile layout of a weight (built by tf_qmm_tile): records indexed [column tile of 16][k tile of 64],
-// each record = 512 bytes of nibbles + 64*(64/group) bytes of (scale, bias) pairs.
+// Weight tile layout (built by tf_qmm_tile): records indexed [column block of 128][k tile of 64]
+// [column tile of 16 inside the block]; a pipeline stage (all 8 column tiles of a block, a few k
+// tiles) is therefore ONE contiguous range and arrives with a single bulk copy. Each record is
+// 512 bytes of nibbles + 64*(64/group) bytes of (scale, bias) pairs.
 //   nibbles: lane (g = lane/4, t = lane%4) owns 16 bytes = 4 words; word s (k-step s) holds, at
-//            nibble j, column 16c + g + 8*(j&1) and k = 64kt + 16t + 4s + {0,2,1,3}[j>>1 & 3]... see
-//            nibble_k() below. (w >> 4i) & 0x000F000F is then register i of the mma A fragment.
+//            nibble j, column 16c + g + 8*(j&1) and input tile_k(t, s, nibble_quad(j)) of the k tile,
+//            so that (w >> 4i) & 0x000F000F is register i of the mma A fragment. K-steps 0,1 cover
+//            inputs 0..31 of the tile and k-steps 2,3 inputs 32..63: a group of 32 is two whole k-steps.
 //   pairs  : for each half-tile h (one per group inside the k tile) and g in 0..7:
 //            bf16 s[16c+g], b[16c+g], s[16c+g+8], b[16c+g+8]   (8 bytes, one load per lane)
-// The B operand (activations) uses the matching k order: lane (g, t) reads x[row g][64kt + 16t ..+16],
-// 32 contiguous bytes, and feeds k-step s with elements 4s..4s+3 of them.
+//
+// Activations arrive "packed" (tf_pack_rows, or written directly by the glue kernels): per k tile,
+// Mp rows (M rounded up to its bucket 8/16/32/64/128, extra rows zero) of 128 bytes (the tile's 64
+// bf16 inputs, with the two 64-byte halves swapped on odd rows so that shared-memory reads spread
+// over all banks), then the tile's group sums as [groups in tile][Mp] fp32. A stage's activations
+// are again one contiguous range.
+//
+// Warp roles in a CTA: 8 consumer warps (one 16-column tile each), one producer thread (bulk
+// copies), one finisher warp that sums parked K segments so the consumers never wait on a fence.
 
 #include "common.cuh"
 
@@ -29,30 +39,31 @@ namespace {
 constexpr int kWorkers = 148;
 constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every row bucket, so that the
                                 // K segments (hence the bits) do not depend on the row count
+constexpr int kWarps = 8;       // consumer warps = column tiles per column block (baked into the layout)
+constexpr int kCols = kWarps * 16;
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 512 + (64 / group) * 64; }
 
 // position inside the 4-element k quad that nibble j of a word carries
 __host__ __device__ constexpr int nibble_quad(int j) { return ((j >> 1) & 1) * 2 + ((j >> 2) & 1); }
+// input (0..63) of a k tile that lane t feeds to k-step s at quad position `quad`
+__host__ __device__ constexpr int tile_k(int t, int s, int quad) { return 32 * (s >> 1) + 8 * t + 4 * (s & 1) + quad; }
 
-template <int G, int MB, int WARPS, int KTS, int STAGES>
+template <int G, int MB, int KTS, int STAGES>
 struct Cfg {
     static constexpr int REC = rec_bytes(G);
     static constexpr int GPT = 64 / G;                 // groups per k tile
-    static constexpr int ROWS = MB * 8;
-    static constexpr int XROW = KTS * 128 + 16;        // bytes per staged activation row (+16: bank spread)
-    static constexpr int W_BYTES = WARPS * KTS * REC;
-    static constexpr int X_BYTES = ROWS * XROW;
-    static constexpr int XS_BYTES = ROWS * KTS * GPT * 4;
-    static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + XS_BYTES + 127) / 128) * 128;
-    static constexpr int COLS = WARPS * 16;            // columns per column block
-    static constexpr int THREADS = (WARPS + 1) * 32;   // consumers + one producer warp
+    static constexpr int ROWS = MB * 8;                // = tf_padded_rows(M) for every M of the bucket
+    static constexpr int XTILE = ROWS * (128 + 4 * GPT);   // packed activation bytes per k tile
+    static constexpr int W_BYTES = kWarps * KTS * REC;
+    static constexpr int X_BYTES = KTS * XTILE;
+    static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + 127) / 128) * 128;
+    static constexpr int THREADS = (kWarps + 2) * 32;   // consumers + producer warp + finisher warp
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
 };
 
 struct Args {
-    const __nv_bfloat16* x;
-    const float* xs;
+    const uint8_t* xp;
     const uint8_t* w;
     void* y;
     int* counters;
@@ -62,25 +73,93 @@ struct Args {
     int f32_out;
 };
 
-// The CTA that owns flattened work item `w` (items split evenly over kWorkers CTAs).
-__host__ __device__ inline int owner_of(long long w, long long total) {
-    return (int)(((w + 1) * kWorkers - 1) / total);
-}
-__host__ __device__ inline long long range_begin(int cta, long long total) { return (long long)cta * total / kWorkers; }
+// Work items (column block, group of kItemTiles k tiles) are split evenly over kWorkers CTAs.
+__host__ __device__ inline int range_begin(int cta, int total) { return (int)((long long)cta * total / kWorkers); }
+__host__ __device__ inline int owner_of(int w, int total) { return (int)((((long long)w + 1) * kWorkers - 1) / total); }
 
-template <int G, int MB, int WARPS, int KTS, int STAGES>
-__global__ void __launch_bounds__((WARPS + 1) * 32, 1) qmm_kernel(const Args a) {
-    using C = Cfg<G, MB, WARPS, KTS, STAGES>;
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int KT = a.K >> 6;                        // k tiles
-    const int KG = a.K / G;                         // groups per row
-    const int NT = (a.N + 15) >> 4;                 // column tiles
-    const int CB = (NT + WARPS - 1) / WARPS;        // column blocks
+constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
+
+// A parked K segment of column block `cb` is complete in global memory: take a ticket; the last of
+// the block's segments to arrive adds them all in k order and writes the output. One warp.
+__device__ void finish_segment(const Args& a, int cb, int SPB, int total, int lane, int* list) {
+    __threadfence();
+    const int cb_begin = cb * SPB;
+    const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
+    int nseg = 0;
+    if (lane == 0) {
+        for (int o = first; o <= last; ++o) {
+            const int ob = range_begin(o, total);
+            if (ob == range_begin(o + 1, total)) continue;       // a worker without work
+            list[nseg++] = 2 * o + (ob < cb_begin ? 1 : 0);      // its slot, in k order
+        }
+        list[kWorkers] = nseg;
+        list[kWorkers + 1] = atomicAdd(a.counters + cb, 1);
+    }
+    __syncwarp();
+    nseg = list[kWorkers];
+    if (list[kWorkers + 1] != nseg - 1) return;
+    __threadfence();
+    const int ncol4 = (min(kCols, a.N - cb * kCols) + 3) >> 2;
+    const int n4 = a.M * (kCols / 4);
+    constexpr int U = 4;          // elements in flight per lane
+    for (int base = lane; base < n4; base += 32 * U) {
+        float4 sum[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < nseg; j += 2) {
+            float4 v[2][U];
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int idx = base + 32 * u;
+                    v[jj][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j + jj < nseg && idx < n4)
+                        v[jj][u] = __ldcg(reinterpret_cast<const float4*>(a.slots + (size_t)list[j + jj] * kSlotFloats) + idx);
+                }
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj)
+                if (j + jj < nseg) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (j + jj == 0) sum[u] = v[jj][u];
+                        else { sum[u].x += v[jj][u].x; sum[u].y += v[jj][u].y; sum[u].z += v[jj][u].z; sum[u].w += v[jj][u].w; }
+                    }
+                }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + 32 * u;
+            if (idx >= n4) continue;
+            const int row = idx / (kCols / 4), c4 = idx - row * (kCols / 4);
+            if (c4 >= ncol4) continue;
+            const float e[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+            const int col = cb * kCols + c4 * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (col + i >= a.N) break;
+                const size_t at = (size_t)row * a.N + col + i;
+                if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = e[i];
+                else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(e[i]);
+            }
+        }
+    }
+    __syncwarp();
+    if (lane == 0) a.counters[cb] = 0;     // leave the counters zero for the next call
+}
+
+template <int G, int MB, int KTS, int STAGES>
+__global__ void __launch_bounds__((kWarps + 2) * 32, (MB <= 2 ? 2 : 1)) qmm_kernel(const Args a) {
+    using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int seg_list[kWorkers + 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KT = a.K >> 6;                              // k tiles
+    const int CB = (a.N + kCols - 1) / kCols;             // column blocks
     const int SPB = (KT + kItemTiles - 1) / kItemTiles;   // schedule items per column block
-    const long long total = (long long)CB * SPB;
-    const long long begin = range_begin(blockIdx.x, total), end = range_begin(blockIdx.x + 1, total);
+    const int total = CB * SPB;
+    const int begin = range_begin(blockIdx.x, total), end = range_begin(blockIdx.x + 1, total);
 
     uint8_t* stage0 = smem;
     const uint32_t bars = smem_u32(smem + STAGES * C::STAGE_BYTES);
@@ -89,86 +168,103 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) qmm_kernel(const Args a) 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 33);             // producer lane 0 (with tx bytes) + 32 async xs arrivals
-            mbar_init(empty_bar(s), WARPS);
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), kWarps);
         }
         mbar_fence_init();
     }
-    // rows beyond M are never copied: keep them zero so the unused accumulator rows stay finite
-    for (int s = 0; s < STAGES; ++s) {
-        uint8_t* xb = stage0 + s * C::STAGE_BYTES + C::W_BYTES;
-        for (int i = threadIdx.x; i < (C::X_BYTES + C::XS_BYTES) / 16; i += C::THREADS)
-            reinterpret_cast<uint4*>(xb)[i] = make_uint4(0, 0, 0, 0);
-    }
-    fence_proxy_async();
     __syncthreads();
-    pdl_wait();                                     // activations come from the previous kernel
+    pdl_launch_dependents();     // the next kernel may be scheduled; it still waits for this one's memory
 
-    if (warp == WARPS) {
-        // ------------------------------- producer warp ----------------------------------------
-        int cnt = 0;
-        for (long long it = begin; it < end; ++it)
-        for (int sub = 0; sub < kItemTiles; sub += KTS) {
-            const int cb = (int)(it / SPB), st = (int)(it % SPB);
-            const int kt0 = st * kItemTiles + sub, nkt = min(KTS, KT - kt0);
-            if (nkt <= 0) break;
-            const int s = cnt % STAGES;
-            const uint32_t parity = ((cnt / STAGES) & 1) ^ 1;
-            mbar_wait(empty_bar(s), parity, a.status);
-            uint8_t* sb = stage0 + s * C::STAGE_BYTES;
-            const int tiles = min(WARPS, NT - cb * WARPS);
-            if (lane == 0) mbar_arrive_expect_tx(full_bar(s), (uint32_t)(tiles * nkt * C::REC + a.M * nkt * 128));
-            __syncwarp();
-            for (int w = lane; w < tiles; w += 32) {
-                const long long ct = (long long)cb * WARPS + w;
-                bulk_g2s(smem_u32(sb + w * KTS * C::REC), a.w + (ct * KT + kt0) * C::REC, (uint32_t)(nkt * C::REC),
-                         full_bar(s));
+    // the first and the last segment of this CTA's range may be parts of a column block
+    const int cb_first = begin < end ? begin / SPB : 0, cb_last = begin < end ? (end - 1) / SPB : 0;
+    const bool part_first = begin > cb_first * SPB || end < (cb_first + 1) * SPB;
+    const bool part_last = cb_last != cb_first && end < (cb_last + 1) * SPB;
+
+    if (warp == kWarps) {
+        // ------------------------------- producer: one thread ----------------------------------
+        // Weights never change during a forward, so the first ring of weight copies is issued before
+        // waiting for the previous kernel; the activations (its output) follow after the wait.
+        if (lane == 0 && begin < end) {
+            int s = 0, issued = 0;
+            uint32_t phase = 1;
+            int cb = cb_first, st = begin - cb * SPB;
+            int early_kt0[STAGES], early_nkt[STAGES];
+            bool waited = false;
+            for (int it = begin; it < end; ++it) {
+                for (int sub = 0; sub < kItemTiles; sub += KTS) {
+                    const int kt0 = st * kItemTiles + sub, nkt = min(KTS, KT - kt0);
+                    if (nkt <= 0) break;
+                    if (issued == STAGES && !waited) {
+                        pdl_wait();
+                        for (int e = 0; e < STAGES; ++e)
+                            bulk_g2s(smem_u32(stage0 + e * C::STAGE_BYTES + C::W_BYTES),
+                                     a.xp + (size_t)early_kt0[e] * C::XTILE, (uint32_t)(early_nkt[e] * C::XTILE), full_bar(e));
+                        waited = true;
+                    }
+                    mbar_wait(empty_bar(s), phase, a.status);
+                    uint8_t* sb = stage0 + s * C::STAGE_BYTES;
+                    const uint32_t wbytes = (uint32_t)(nkt * kWarps * C::REC), xbytes = (uint32_t)(nkt * C::XTILE);
+                    mbar_arrive_expect_tx(full_bar(s), wbytes + xbytes);
+                    bulk_g2s(smem_u32(sb), a.w + ((size_t)cb * KT + kt0) * (kWarps * C::REC), wbytes, full_bar(s));
+                    if (waited) bulk_g2s(smem_u32(sb + C::W_BYTES), a.xp + (size_t)kt0 * C::XTILE, xbytes, full_bar(s));
+                    else { early_kt0[issued] = kt0; early_nkt[issued] = nkt; }
+                    ++issued;
+                    if (++s == STAGES) { s = 0; phase ^= 1; }
+                }
+                if (++st == SPB) { st = 0; ++cb; }
             }
-            for (int r = lane; r < a.M; r += 32)
-                bulk_g2s(smem_u32(sb + C::W_BYTES + r * C::XROW), a.x + (size_t)r * a.K + (size_t)kt0 * 64,
-                         (uint32_t)(nkt * 128), full_bar(s));
-            const int ng = nkt * C::GPT;
-            for (int i = lane; i < a.M * ng; i += 32) {
-                const int r = i / ng, j = i - r * ng;
-                cp_async4(smem_u32(sb + C::W_BYTES + C::X_BYTES + (r * KTS * C::GPT + j) * 4),
-                          a.xs + (size_t)r * KG + (size_t)kt0 * C::GPT + j);
+            if (!waited) {
+                pdl_wait();
+                for (int e = 0; e < issued; ++e)
+                    bulk_g2s(smem_u32(stage0 + e * C::STAGE_BYTES + C::W_BYTES), a.xp + (size_t)early_kt0[e] * C::XTILE,
+                             (uint32_t)(early_nkt[e] * C::XTILE), full_bar(e));
             }
-            cp_async_mbar_arrive_noinc(full_bar(s));
-            ++cnt;
         }
-        // drain: nothing may still be landing in shared memory when the CTA retires
-        cp_async_wait<0>();
+        return;
+    }
+    pdl_wait();                  // everything below reads or writes what other kernels produce or read
+    if (begin >= end) return;
+    if (warp == kWarps + 1) {
+        // ------------------- finisher: sums parked segments while the consumers go on -----------
+        if (part_first) {
+            named_bar_sync(2, (kWarps + 1) * 32);
+            finish_segment(a, cb_first, SPB, total, lane, seg_list);
+        }
+        if (part_last) {
+            named_bar_sync(3, (kWarps + 1) * 32);
+            finish_segment(a, cb_last, SPB, total, lane, seg_list);
+        }
         return;
     }
 
     // ----------------------------------- consumer warps ---------------------------------------
     const int g = lane >> 2, t = lane & 3;
+    const int xlane = g * 128 + ((t * 16) ^ ((g & 1) << 6));   // this lane's B-operand bytes inside a row block
     float acc[MB][4];
-    int cnt = 0;
-    long long it = begin;
+    int s = 0;
+    uint32_t phase = 0;
+    int it = begin;
     while (it < end) {
-        const int cb = (int)(it / SPB);
-        const long long cb_begin = (long long)cb * SPB, cb_end = cb_begin + SPB;
-        const long long seg_end = cb_end < end ? cb_end : end;
-        const int ct = cb * WARPS + warp;
-        const bool live = ct < NT;
+        const int cb = it / SPB;
+        const int cb_begin = cb * SPB, cb_end = cb_begin + SPB;
+        const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
         for (int rb = 0; rb < MB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
 
         for (; it < seg_end; ++it)
         for (int sub = 0; sub < kItemTiles; sub += KTS) {
-            const int st = (int)(it - cb_begin);
-            const int nkt = min(KTS, KT - (st * kItemTiles + sub));
+            const int nkt = min(KTS, KT - ((it - cb_begin) * kItemTiles + sub));
             if (nkt <= 0) break;
-            const int s = cnt % STAGES;
-            mbar_wait(full_bar(s), (cnt / STAGES) & 1, a.status);
-            if (live) {
-                const uint8_t* sb = stage0 + s * C::STAGE_BYTES;
-                const uint8_t* wrec = sb + warp * KTS * C::REC;
-                const uint8_t* xrow = sb + C::W_BYTES;
-                const float* xsst = reinterpret_cast<const float*>(sb + C::W_BYTES + C::X_BYTES);
-                for (int kt = 0; kt < nkt; ++kt) {
-                    const uint4 wq = *reinterpret_cast<const uint4*>(wrec + kt * C::REC + lane * 16);
+            mbar_wait(full_bar(s), phase, a.status);
+            const uint8_t* sb = stage0 + s * C::STAGE_BYTES;
+            const uint8_t* wrec = sb + warp * C::REC;
+            const uint8_t* xst = sb + C::W_BYTES;
+#pragma unroll
+            for (int kt = 0; kt < KTS; ++kt) {
+                if (kt < nkt) {
+                    const uint8_t* rec = wrec + kt * (kWarps * C::REC);
+                    const uint4 wq = *reinterpret_cast<const uint4*>(rec + lane * 16);
                     const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
                     uint32_t af[4][4];
 #pragma unroll
@@ -178,112 +274,81 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) qmm_kernel(const Args a) 
                     float sc[C::GPT][2], bi[C::GPT][2];
 #pragma unroll
                     for (int h = 0; h < C::GPT; ++h) {
-                        const uint2 p = *reinterpret_cast<const uint2*>(wrec + kt * C::REC + 512 + h * 64 + g * 8);
+                        const uint2 p = *reinterpret_cast<const uint2*>(rec + 512 + h * 64 + g * 8);
                         sc[h][0] = bf16_lo(p.x); bi[h][0] = bf16_hi(p.x);
                         sc[h][1] = bf16_lo(p.y); bi[h][1] = bf16_hi(p.y);
                     }
+                    const uint8_t* xt = xst + kt * C::XTILE;
+                    const float* xsums = reinterpret_cast<const float*>(xt + C::ROWS * 128) + 2 * t;
 #pragma unroll
                     for (int rb = 0; rb < MB; ++rb) {
-                        const uint8_t* xp = xrow + (rb * 8 + g) * C::XROW + kt * 128 + t * 32;
-                        const uint4 x0 = *reinterpret_cast<const uint4*>(xp);
-                        const uint4 x1 = *reinterpret_cast<const uint4*>(xp + 16);
+                        const uint4 x0 = *reinterpret_cast<const uint4*>(xt + rb * 1024 + xlane);
+                        const uint4 x1 = *reinterpret_cast<const uint4*>(xt + rb * 1024 + (xlane ^ 64));
                         const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                        constexpr int SPG = 4 / C::GPT;   // k-steps per group
 #pragma unroll
                         for (int h = 0; h < C::GPT; ++h) {
-                            const float xs0 = xsst[(rb * 8 + 2 * t) * KTS * C::GPT + kt * C::GPT + h];
-                            const float xs1 = xsst[(rb * 8 + 2 * t + 1) * KTS * C::GPT + kt * C::GPT + h];
-                            float p[4] = {-128.f * xs0, -128.f * xs1, -128.f * xs0, -128.f * xs1};
-                            constexpr int SPG = 4 / C::GPT;   // k-steps per group
+                            const float2 xs = *reinterpret_cast<const float2*>(xsums + h * C::ROWS + rb * 8);
+                            float p[4] = {-128.f * xs.x, -128.f * xs.y, -128.f * xs.x, -128.f * xs.y};
 #pragma unroll
                             for (int s4 = h * SPG; s4 < (h + 1) * SPG; ++s4)
                                 mma_bf16_16816(p, af[s4], xb[2 * s4], xb[2 * s4 + 1], p);
-                            acc[rb][0] = __fmaf_rn(bi[h][0], xs0, __fmaf_rn(sc[h][0], p[0], acc[rb][0]));
-                            acc[rb][1] = __fmaf_rn(bi[h][0], xs1, __fmaf_rn(sc[h][0], p[1], acc[rb][1]));
-                            acc[rb][2] = __fmaf_rn(bi[h][1], xs0, __fmaf_rn(sc[h][1], p[2], acc[rb][2]));
-                            acc[rb][3] = __fmaf_rn(bi[h][1], xs1, __fmaf_rn(sc[h][1], p[3], acc[rb][3]));
+                            acc[rb][0] = __fmaf_rn(bi[h][0], xs.x, __fmaf_rn(sc[h][0], p[0], acc[rb][0]));
+                            acc[rb][1] = __fmaf_rn(bi[h][0], xs.y, __fmaf_rn(sc[h][0], p[1], acc[rb][1]));
+                            acc[rb][2] = __fmaf_rn(bi[h][1], xs.x, __fmaf_rn(sc[h][1], p[2], acc[rb][2]));
+                            acc[rb][3] = __fmaf_rn(bi[h][1], xs.y, __fmaf_rn(sc[h][1], p[3], acc[rb][3]));
                         }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(s));
-            ++cnt;
+            if (++s == STAGES) { s = 0; phase ^= 1; }
         }
 
-        // ---- segment done: whole column block -> write; part of one -> park it, last one sums ----
-        const long long seg_begin = (cb_begin > begin) ? cb_begin : begin;
+        // ---- segment done: whole column block -> write; part of one -> park it for the finisher ----
         const bool whole = (seg_begin == cb_begin) && (seg_end == cb_end);
-        const int col0 = ct * 16 + g;
+        const int col0 = cb * kCols + warp * 16 + g;
         if (whole) {
-            if (live) {
 #pragma unroll
-                for (int rb = 0; rb < MB; ++rb)
+            for (int rb = 0; rb < MB; ++rb)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = rb * 8 + 2 * t + (i & 1), col = col0 + (i >> 1) * 8;
-                        if (row < a.M && col < a.N) {
-                            if (a.f32_out) reinterpret_cast<float*>(a.y)[(size_t)row * a.N + col] = acc[rb][i];
-                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)row * a.N + col] = f2bf(acc[rb][i]);
-                        }
+                for (int i = 0; i < 4; ++i) {
+                    const int row = rb * 8 + 2 * t + (i & 1), col = col0 + (i >> 1) * 8;
+                    if (row < a.M && col < a.N) {
+                        if (a.f32_out) reinterpret_cast<float*>(a.y)[(size_t)row * a.N + col] = acc[rb][i];
+                        else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)row * a.N + col] = f2bf(acc[rb][i]);
                     }
-            }
+                }
         } else {
             // slot 2*cta + 1 when this CTA entered the column block from an earlier one, else 2*cta
-            float* slot = a.slots + (size_t)(2 * blockIdx.x + (begin < cb_begin ? 1 : 0)) * (TF_QMM_MAX_ROWS * C::COLS);
-            if (live) {
+            const int later = begin < cb_begin ? 1 : 0;
+            float* slot = a.slots + (size_t)(2 * blockIdx.x + later) * kSlotFloats;
 #pragma unroll
-                for (int rb = 0; rb < MB; ++rb)
+            for (int rb = 0; rb < MB; ++rb)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = rb * 8 + 2 * t + (i & 1);
-                        if (row < a.M) __stcg(slot + row * C::COLS + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
-                    }
-            }
-            __threadfence();
-            named_bar_sync(1, WARPS * 32);
-            __shared__ int ticket_s;
-            const int first = owner_of(cb_begin, total), last = owner_of(cb_end - 1, total);
-            if (threadIdx.x == 0) ticket_s = atomicAdd(a.counters + cb, 1);
-            named_bar_sync(1, WARPS * 32);
-            const bool reducer = ticket_s == last - first;
-            named_bar_sync(1, WARPS * 32);       // everyone has read the ticket before it can be rewritten
-            if (reducer) {
-                __threadfence();
-                const int ncol = min(C::COLS, a.N - cb * C::COLS);
-                for (int idx = threadIdx.x; idx < a.M * C::COLS; idx += WARPS * 32) {
-                    const int row = idx / C::COLS, col = idx - row * C::COLS;
-                    if (col >= ncol) continue;
-                    float sum = 0.f;
-                    for (int o = first; o <= last; ++o) {
-                        const int which = range_begin(o, total) < cb_begin ? 1 : 0;
-                        const float v = __ldcg(a.slots + (size_t)(2 * o + which) * (TF_QMM_MAX_ROWS * C::COLS) +
-                                               row * C::COLS + col);
-                        sum = (o == first) ? v : sum + v;
-                    }
-                    const size_t at = (size_t)row * a.N + cb * C::COLS + col;
-                    if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = sum;
-                    else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(sum);
+                for (int i = 0; i < 4; ++i) {
+                    const int row = rb * 8 + 2 * t + (i & 1);
+                    if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
                 }
-                if (threadIdx.x == 0) a.counters[cb] = 0;     // leave the counters zero for the next call
-            }
+            // hand over to the finisher warp without waiting for it
+            if (cb == cb_first) asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");
+            else asm volatile("bar.arrive 3, %0;" ::"r"((kWarps + 1) * 32) : "memory");
         }
     }
-    pdl_launch_dependents();
 }
 
-template <int G, int MB, int WARPS, int KTS, int STAGES>
+template <int G, int MB, int KTS, int STAGES>
 int launch(const Args& a, cudaStream_t stream) {
-    using C = Cfg<G, MB, WARPS, KTS, STAGES>;
+    using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(C::SMEM <= 227 * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<G, MB, WARPS, KTS, STAGES>;
+    auto kern = qmm_kernel<G, MB, KTS, STAGES>;
     static bool configured = false;   // per instantiation; the attribute is per function and idempotent
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
             return TF_ECUDA;
         configured = true;
     }
-    const int NT = (a.N + 15) / 16, CB = (NT + WARPS - 1) / WARPS;
-    if (CB * 4 > TF_QMM_COUNTER_BYTES) return TF_EINVAL;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kWorkers);
     cfg.blockDim = dim3(C::THREADS);
@@ -298,35 +363,37 @@ int launch(const Args& a, cudaStream_t stream) {
     return TF_OK;
 }
 
-constexpr int kWarps = 8;   // consumer warps = 128 columns per column block, for every row bucket
-
 template <int G>
 int dispatch(const Args& a, cudaStream_t stream) {
-    if (a.M <= 8) return launch<G, 1, kWarps, 4, 8>(a, stream);
-    if (a.M <= 16) return launch<G, 2, kWarps, 4, 6>(a, stream);
-    if (a.M <= 32) return launch<G, 4, kWarps, 4, 5>(a, stream);
-    if (a.M <= 64) return launch<G, 8, kWarps, 2, 5>(a, stream);
-    return launch<G, 16, kWarps, 2, 4>(a, stream);
+    if (a.M <= 8) return launch<G, 1, 4, 4>(a, stream);      // two CTAs fit an SM: the next kernel's
+    if (a.M <= 16) return launch<G, 2, 4, 4>(a, stream);     // weight prefetch overlaps this one's tail
+    if (a.M <= 32) return launch<G, 4, 4, 6>(a, stream);
+    if (a.M <= 64) return launch<G, 8, 2, 6>(a, stream);
+    return launch<G, 16, 2, 5>(a, stream);
 }
 
 // ---- relayout kernels: one thread per output word / pair -----------------------------------------
+__device__ __forceinline__ size_t record_offset(int col_tile, int kt, int KT, int REC) {
+    return (((size_t)(col_tile / kWarps) * KT + kt) * kWarps + (col_tile % kWarps)) * REC;
+}
+
 __global__ void tile_kernel(const uint32_t* words, const uint16_t* scales, const uint16_t* biases, uint8_t* out,
                             int N, int K, int G) {
-    const int KT = K >> 6, NT = (N + 15) >> 4, REC = rec_bytes(G), GPT = 64 / G;
-    const long long recs = (long long)NT * KT;
+    const int KT = K >> 6, CB = (N + kCols - 1) / kCols, REC = rec_bytes(G), GPT = 64 / G;
+    const long long recs = (long long)CB * kWarps * KT;
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int per = 128 + 16 * GPT;                 // threads per record: 128 words + 16*GPT (s,b) pairs
     if (id >= recs * per) return;
     const long long rec = id / per;
     const int e = (int)(id % per);
     const int c = (int)(rec / KT), kt = (int)(rec % KT);
-    uint8_t* r = out + rec * REC;
+    uint8_t* r = out + record_offset(c, kt, KT, REC);
     if (e < 128) {
         const int lane = e >> 2, s = e & 3, g = lane >> 2, t = lane & 3;
         uint32_t w = 0;
         for (int j = 0; j < 8; ++j) {
             const int col = 16 * c + g + 8 * (j & 1);
-            const int k = 64 * kt + 16 * t + 4 * s + nibble_quad(j);
+            const int k = 64 * kt + tile_k(t, s, nibble_quad(j));
             uint32_t q = 0;
             if (col < N) q = (words[(size_t)col * (K >> 3) + (k >> 3)] >> (4 * (k & 7))) & 0xFu;
             w |= q << (4 * j);
@@ -351,11 +418,12 @@ __global__ void untile_kernel(const uint8_t* in, uint32_t* words, uint16_t* scal
         const int col = (int)(id / (K >> 3)), wi = (int)(id % (K >> 3));
         uint32_t w = 0;
         for (int i = 0; i < 8; ++i) {
-            const int k = wi * 8 + i, kt = k >> 6, kin = k & 63, t = kin >> 4, s = (kin >> 2) & 3, quad = kin & 3;
+            const int k = wi * 8 + i, kt = k >> 6, kin = k & 63, t = (kin >> 3) & 3, s = 2 * (kin >> 5) + ((kin >> 2) & 1),
+                      quad = kin & 3;
             const int c = col >> 4, cin = col & 15, g = cin & 7, hi = cin >> 3;
             // inverse of nibble_quad: quad {0,1,2,3} sits at (j>>1) = {0,2,1,3}
             const int j = hi + 2 * (((quad & 1) << 1) | (quad >> 1));
-            const uint32_t v = reinterpret_cast<const uint32_t*>(in + ((long long)c * KT + kt) * REC)[(g * 4 + t) * 4 + s];
+            const uint32_t v = reinterpret_cast<const uint32_t*>(in + record_offset(c, kt, KT, REC))[(g * 4 + t) * 4 + s];
             w |= ((v >> (4 * j)) & 0xFu) << (4 * i);
         }
         words[id] = w;
@@ -364,27 +432,26 @@ __global__ void untile_kernel(const uint8_t* in, uint32_t* words, uint16_t* scal
         const int col = (int)(p / (K / G)), grp = (int)(p % (K / G));
         const int kt = grp / GPT, h = grp % GPT, c = col >> 4, cin = col & 15, g = cin & 7, hi = cin >> 3;
         const uint16_t* src =
-            reinterpret_cast<const uint16_t*>(in + ((long long)c * KT + kt) * REC + 512 + h * 64 + g * 8 + hi * 4);
+            reinterpret_cast<const uint16_t*>(in + record_offset(c, kt, KT, REC) + 512 + h * 64 + g * 8 + hi * 4);
         scales[p] = src[0];
         biases[p] = src[1];
     }
 }
 
+// Row-major bf16 rows -> packed activations (+ group sums). One lane per 8 contiguous inputs:
+// sequential sum of 8, then a pairwise tree across the G/8 lanes of a group.
 template <int G>
-__global__ void group_sums_kernel(const __nv_bfloat16* x, float* xs, int M, int K) {
-    // one lane per 8 contiguous inputs: sequential sum of 8, then a pairwise tree across G/8 lanes
+__global__ void pack_rows_kernel(const __nv_bfloat16* x, uint8_t* xp, float* xs_out, int M, int K) {
+    const int Mp = tf_padded_rows(M);
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long chunks = (long long)M * (K >> 3);
-    float s = 0.f;
-    if (id < chunks) {
-        const uint4 v = reinterpret_cast<const uint4*>(x)[id];
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { s += bf16_lo(u[i]); s += bf16_hi(u[i]); }
-    }
-#pragma unroll
-    for (int o = 1; o < G / 8; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (id < chunks && (id & (G / 8 - 1)) == 0) xs[id / (G / 8)] = s;
+    const long long chunks = (long long)Mp * (K >> 3);
+    const int row = (int)(id / (K >> 3)), c = (int)(id % (K >> 3));       // chunk c = inputs 8c..8c+7
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (id < chunks && row < M) v = reinterpret_cast<const uint4*>(x)[(size_t)row * (K >> 3) + c];
+    const float s = group_sum8<G>(v);
+    if (id >= chunks) return;
+    packed_store<G>(xp, Mp, row, c, v, s);
+    if ((c & (G / 8 - 1)) == 0 && xs_out != nullptr && row < M) xs_out[(size_t)row * (K / G) + c / (G / 8)] = s;
 }
 
 }  // namespace
@@ -397,28 +464,33 @@ int tf_qmm_workers(void) { return tf::kWorkers; }
 
 size_t tf_qmm_tiled_bytes(int N, int K, int group) {
     if (N <= 0 || K <= 0 || K % 64 || (group != 64 && group != 32)) return 0;
-    return (size_t)((N + 15) / 16) * (K / 64) * tf::rec_bytes(group);
+    return (size_t)((N + tf::kCols - 1) / tf::kCols) * tf::kWarps * (K / 64) * tf::rec_bytes(group);
 }
 
-size_t tf_qmm_scratch_bytes(int M, int N, int K, int group) {
-    (void)M; (void)N; (void)K; (void)group;
+size_t tf_packed_bytes(int M, int K, int group) {
+    if (M <= 0 || K <= 0 || K % 64 || (group != 64 && group != 32)) return 0;
+    return (size_t)(K / 64) * tf::tf_padded_rows(M) * (128 + 4 * (64 / group));
+}
+
+size_t tf_qmm_scratch_bytes(void) {
     // counters + two parked partial blocks (128 rows x 128 columns fp32) per worker
-    return TF_QMM_COUNTER_BYTES + (size_t)2 * tf::kWorkers * TF_QMM_MAX_ROWS * (tf::kWarps * 16) * sizeof(float);
+    return TF_QMM_COUNTER_BYTES + (size_t)2 * tf::kWorkers * TF_QMM_MAX_ROWS * tf::kCols * sizeof(float);
 }
 
-int tf_qmm(const void* x, const void* xs, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M,
-           int N, int K, int group, int flags, int* status, void* stream) {
+int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N, int K,
+           int group, int flags, int* status, void* stream) {
     if (M < 1 || M > TF_QMM_MAX_ROWS || N < 1 || K < 64 || K % 64) return TF_EINVAL;
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
-    if (!x || !xs || !w_tiled || !y) return TF_EINVAL;
-    if (((uintptr_t)x | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
-    if (((uintptr_t)xs | (uintptr_t)y) & 3) return TF_EALIGN;
+    if (!x_packed || !w_tiled || !y) return TF_EINVAL;
+    const long long CB = (N + tf::kCols - 1) / tf::kCols, SPB = (K / 64 + tf::kItemTiles - 1) / tf::kItemTiles;
+    if (CB * 4 > TF_QMM_COUNTER_BYTES || CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
+    if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
+    if ((uintptr_t)y & 3) return TF_EALIGN;
     if (!scratch || ((uintptr_t)scratch & 255)) return TF_ESCRATCH;
-    if (scratch_bytes < tf_qmm_scratch_bytes(M, N, K, group)) return TF_ESCRATCH;
+    if (scratch_bytes < tf_qmm_scratch_bytes()) return TF_ESCRATCH;
     tf::Args a;
-    a.x = static_cast<const __nv_bfloat16*>(x);
-    a.xs = static_cast<const float*>(xs);
+    a.xp = static_cast<const uint8_t*>(x_packed);
     a.w = static_cast<const uint8_t*>(w_tiled);
     a.y = y;
     a.counters = static_cast<int*>(scratch);
@@ -434,7 +506,7 @@ int tf_qmm_tile(const void* words, const void* scales, const void* biases, void*
                 void* stream) {
     if (N < 1 || K < 64 || K % 64 || (group != 64 && group != 32)) return TF_EINVAL;
     if (!words || !scales || !biases || !w_tiled) return TF_EINVAL;
-    const long long recs = (long long)((N + 15) / 16) * (K / 64);
+    const long long recs = (long long)((N + tf::kCols - 1) / tf::kCols) * tf::kWarps * (K / 64);
     const long long threads = recs * (128 + 16 * (64 / group));
     tf::tile_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint32_t*>(words), static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
@@ -453,15 +525,16 @@ int tf_qmm_untile(const void* w_tiled, void* words, void* scales, void* biases, 
     return cudaGetLastError() == cudaSuccess ? TF_OK : TF_ECUDA;
 }
 
-int tf_group_sums(const void* x, void* xs, int M, int K, int group, void* stream) {
+int tf_pack_rows(const void* x, void* x_packed, void* xs, int M, int K, int group, void* stream) {
     if (M < 1 || K < 64 || K % 64 || (group != 64 && group != 32)) return TF_EINVAL;
-    if (!x || !xs) return TF_EINVAL;
-    if ((uintptr_t)x & 15) return TF_EALIGN;
-    const long long chunks = (long long)M * (K / 8);
+    if (!x || !x_packed) return TF_EINVAL;
+    if (((uintptr_t)x | (uintptr_t)x_packed) & 15) return TF_EALIGN;
+    const long long chunks = (long long)tf::tf_padded_rows(M) * (K / 8);
     const unsigned blocks = (unsigned)((chunks + 255) / 256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (group == 64) tf::group_sums_kernel<64><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<float*>(xs), M, K);
-    else tf::group_sums_kernel<32><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<float*>(xs), M, K);
+    auto* xi = static_cast<const __nv_bfloat16*>(x);
+    if (group == 64) tf::pack_rows_kernel<64><<<blocks, 256, 0, st>>>(xi, static_cast<uint8_t*>(x_packed), static_cast<float*>(xs), M, K);
+    else tf::pack_rows_kernel<32><<<blocks, 256, 0, st>>>(xi, static_cast<uint8_t*>(x_packed), static_cast<float*>(xs), M, K);
     return cudaGetLastError() == cudaSuccess ? TF_OK : TF_ECUDA;
 }
 

@@ -99,7 +99,7 @@ def segments(n: int, k: int) -> list[list[tuple[int, int]]]:
 
     kts = ITEM_TILES
     kt = k // 64
-    cb = -(-(-(-n // 16)) // (COLUMN_BLOCK // 16))
+    cb = -(-n // COLUMN_BLOCK)
     spb = -(-kt // kts)
     total = cb * spb
     bounds = [i * total // WORKERS for i in range(WORKERS + 1)]
@@ -121,18 +121,56 @@ def split_k(n: int, k: int) -> int:
     return max(len(s) for s in segments(n, k))
 
 
+@dataclass
+class Packed:
+    """M activation rows in the form the lane matmul reads (``tf_pack_rows``): per 64-input k tile,
+    the rows' 128-byte slices, then that tile's group sums. Glue kernels write it directly."""
+
+    data: torch.Tensor       # uint8, tf_packed_bytes(m, k, group)
+    m: int
+    k: int
+    group: int
+
+
+def padded_rows(m: int) -> int:
+    """Rows a packed buffer holds for m rows: the row bucket (8, 16, 32, 64, 128) the kernel runs m in."""
+
+    for b in (8, 16, 32, 64, 128):
+        if m <= b:
+            return b
+    raise ValueError(f"at most {MAX_ROWS} rows per packed buffer, got {m}")
+
+
+def packed_bytes(m: int, k: int, group: int) -> int:
+    return (k // 64) * padded_rows(m) * (128 + 4 * (64 // group))
+
+
+def new_packed(m: int, k: int, group: int, device) -> Packed:
+    return Packed(torch.empty(packed_bytes(m, k, group), dtype=torch.uint8, device=device), m, k, group)
+
+
+def pack_rows(x: torch.Tensor, group: int = 64, *, want_sums: bool = False):
+    """(M, K) bf16 row-major -> ``Packed`` (and, with ``want_sums``, the (M, K/group) fp32 group sums)."""
+
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("pack_rows: x must be a 2-D bf16 tensor")
+    _lib.need_cuda(x)
+    m, k = x.shape
+    if m < 1 or k % 64 or group not in (32, 64):
+        raise ValueError(f"pack_rows: unsupported shape {tuple(x.shape)} / group {group}")
+    x = x.contiguous()
+    out = new_packed(m, k, group, x.device)
+    xs = torch.empty((m, k // group), dtype=torch.float32, device=x.device) if want_sums else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().tf_pack_rows(x.data_ptr(), out.data.data_ptr(), _lib.ptr(xs), m, k, group,
+                                            _lib.stream()), "pack_rows")
+    return (out, xs) if want_sums else out
+
+
 def group_sums(x: torch.Tensor, group: int = 64) -> torch.Tensor:
     """(M, K) bf16 -> (M, K/group) fp32 sums of each input group (reference: ``qmm.group_sums``)."""
 
-    if x.dim() != 2 or x.dtype != torch.bfloat16:
-        raise ValueError("group_sums: x must be a 2-D bf16 tensor")
-    _lib.need_cuda(x)
-    m, k = x.shape
-    x = x.contiguous()
-    xs = torch.empty((m, k // group), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
-        _lib.check(_lib.load().tf_group_sums(x.data_ptr(), xs.data_ptr(), m, k, group, _lib.stream()), "group_sums")
-    return xs
+    return pack_rows(x, group, want_sums=True)[1]
 
 
 _scratch: dict[tuple[int, int], torch.Tensor] = {}
@@ -144,53 +182,56 @@ def scratch_for(device: torch.device) -> torch.Tensor:
     key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(key)
     if buf is None:
-        size = _lib.load().tf_qmm_scratch_bytes(MAX_ROWS, 1, 64, 64)
-        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        buf = torch.zeros(_lib.load().tf_qmm_scratch_bytes(), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
 
 
-def lane_matmul(x: torch.Tensor, weight: QWeight, xs: torch.Tensor | None = None, *, f32: bool = False,
+def lane_matmul(x: torch.Tensor | Packed, weight: QWeight, *, f32: bool = False,
                 out: torch.Tensor | None = None) -> torch.Tensor:
-    """x (..., K) bf16 times the 4-bit ``weight`` (N, K) transposed -> (..., N) bf16.
+    """x (..., K) bf16 — or rows already ``Packed`` by the producing kernel — times the 4-bit
+    ``weight`` (N, K) transposed -> (..., N) bf16.
 
-    ``xs``: x's group sums when the producing kernel already wrote them. ``f32``: return the
-    unrounded fp32 sums (a tensor-parallel rank's partial). More than ``MAX_ROWS`` rows run as
-    several launches; a row's bits do not depend on which launch it rides in.
+    ``f32``: return the unrounded fp32 sums (a tensor-parallel rank's partial). More than
+    ``MAX_ROWS`` rows run as several launches; a row's bits do not depend on which launch it rides in.
     """
 
-    if x.dtype != torch.bfloat16:
-        raise ValueError("lane_matmul: x must be bf16")
-    if x.shape[-1] != weight.k:
-        raise ValueError(f"lane_matmul: weight (N={weight.n}, K={weight.k}) does not match K={x.shape[-1]}")
-    _lib.need_cuda(x)
-    lead = x.shape[:-1]
-    x2 = x.reshape(-1, weight.k).contiguous()
-    m = x2.shape[0]
-    if m < 1:
-        raise ValueError("lane_matmul: needs at least one row")
-    if xs is None:
-        xs = group_sums(x2, weight.group)
-    xs = xs.reshape(m, weight.k // weight.group)
-    if xs.dtype != torch.float32 or not xs.is_contiguous():
-        raise ValueError("lane_matmul: xs must be contiguous fp32 (M, K/group)")
+    lib = _lib.load()
+    if isinstance(x, Packed):
+        if x.k != weight.k or x.group != weight.group:
+            raise ValueError(f"lane_matmul: packed rows (K={x.k}, group {x.group}) do not match the weight "
+                             f"(K={weight.k}, group {weight.group})")
+        if x.m > MAX_ROWS:
+            raise ValueError(f"lane_matmul: packed input holds {x.m} rows, at most {MAX_ROWS} per call")
+        chunks, lead, m, dev = [x], (x.m,), x.m, x.data.device
+    else:
+        if x.dtype != torch.bfloat16:
+            raise ValueError("lane_matmul: x must be bf16")
+        if x.shape[-1] != weight.k:
+            raise ValueError(f"lane_matmul: weight (N={weight.n}, K={weight.k}) does not match K={x.shape[-1]}")
+        _lib.need_cuda(x)
+        lead, dev = x.shape[:-1], x.device
+        x2 = x.reshape(-1, weight.k)
+        m = x2.shape[0]
+        if m < 1:
+            raise ValueError("lane_matmul: needs at least one row")
+        chunks = [pack_rows(x2[r0:r0 + MAX_ROWS], weight.group) for r0 in range(0, m, MAX_ROWS)]
     dtype = torch.float32 if f32 else torch.bfloat16
     if out is None:
-        out = torch.empty((m, weight.n), dtype=dtype, device=x.device)
+        out = torch.empty((m, weight.n), dtype=dtype, device=dev)
     elif out.shape != (m, weight.n) or out.dtype != dtype or not out.is_contiguous():
         raise ValueError("lane_matmul: out has the wrong shape or dtype")
-    lib = _lib.load()
-    scratch = scratch_for(x.device)
-    st = _lib.status(x.device)
-    with torch.cuda.device(x.device):
-        for r0 in range(0, m, MAX_ROWS):
-            r1 = min(m, r0 + MAX_ROWS)
-            _lib.check(lib.tf_qmm(x2[r0:r1].data_ptr(), xs[r0:r1].data_ptr(), weight.tiled.data_ptr(),
-                                  out[r0:r1].data_ptr(), scratch.data_ptr(), scratch.numel(), r1 - r0, weight.n,
-                                  weight.k, weight.group, 1 if f32 else 0, st.word.data_ptr(), _lib.stream()),
-                       "lane_matmul")
+    scratch = scratch_for(dev)
+    st = _lib.status(dev)
+    with torch.cuda.device(dev):
+        r0 = 0
+        for c in chunks:
+            _lib.check(lib.tf_qmm(c.data.data_ptr(), weight.tiled.data_ptr(), out[r0:r0 + c.m].data_ptr(),
+                                  scratch.data_ptr(), scratch.numel(), c.m, weight.n, weight.k, weight.group,
+                                  1 if f32 else 0, st.word.data_ptr(), _lib.stream()), "lane_matmul")
+            r0 += c.m
     return out.reshape(*lead, weight.n)
 
 
-__all__ = ["MAX_ROWS", "QWeight", "group_sums", "lane_matmul", "pack_scales", "segments", "split_k", "tile_weight",
-           "untile_weight"]
+__all__ = ["MAX_ROWS", "Packed", "QWeight", "group_sums", "lane_matmul", "new_packed", "pack_rows", "pack_scales",
+           "packed_bytes", "segments", "split_k", "tile_weight", "untile_weight"]

@@ -29,9 +29,10 @@ def test_pure_host_entry_points(lib):
     # 16-column x 64-k records of 576 bytes (group 64) / 640 bytes (group 32): 4.5 and 5 bits a weight
     assert lib.tf_qmm_tiled_bytes(17408, 5120, 64) == 17408 * 5120 * 9 // 16
     assert lib.tf_qmm_tiled_bytes(768, 2048, 32) == 768 * 2048 * 5 // 8
-    assert lib.tf_qmm_tiled_bytes(40, 64, 64) == 3 * 576          # columns padded to 16
+    assert lib.tf_qmm_tiled_bytes(40, 64, 64) == 8 * 576          # columns padded to a 128-column block
+    assert lib.tf_packed_bytes(8, 5120, 64) == 80 * 8 * 132 and lib.tf_packed_bytes(9, 2048, 32) == 32 * 16 * 136
     assert lib.tf_qmm_tiled_bytes(16, 100, 64) == 0               # K must be a multiple of 64
-    assert lib.tf_qmm_scratch_bytes(8, 17408, 5120, 64) > 16384
+    assert lib.tf_qmm_scratch_bytes() > 16384
 
 
 def test_bad_arguments_are_refused_before_any_launch(lib):
@@ -40,14 +41,14 @@ def test_bad_arguments_are_refused_before_any_launch(lib):
     buf = (ctypes.c_char * 4096)()
     p = ctypes.addressof(buf)
     p = (p + 255) & ~255
-    big = lib.tf_qmm_scratch_bytes(8, 64, 64, 64)
-    assert lib.tf_qmm(p, p, p, p, p, big, 0, 64, 64, 64, 0, None, None) == _lib.TF_EINVAL      # no rows
-    assert lib.tf_qmm(p, p, p, p, p, big, 129, 64, 64, 64, 0, None, None) == _lib.TF_EINVAL    # too many rows
-    assert lib.tf_qmm(p, p, p, p, p, big, 8, 64, 96, 64, 0, None, None) == _lib.TF_EINVAL      # K % 64
-    assert lib.tf_qmm(p, p, p, p, p, big, 8, 64, 64, 16, 0, None, None) == _lib.TF_EINVAL      # group
-    assert lib.tf_qmm(p + 2, p, p, p, p, big, 8, 64, 64, 64, 0, None, None) == _lib.TF_EALIGN
-    assert lib.tf_qmm(p, p, p, p, None, big, 8, 64, 64, 64, 0, None, None) == _lib.TF_ESCRATCH
-    assert lib.tf_qmm(p, p, p, p, p, 16, 8, 64, 64, 64, 0, None, None) == _lib.TF_ESCRATCH
+    big = lib.tf_qmm_scratch_bytes()
+    assert lib.tf_qmm(p, p, p, p, big, 0, 64, 64, 64, 0, None, None) == _lib.TF_EINVAL      # no rows
+    assert lib.tf_qmm(p, p, p, p, big, 129, 64, 64, 64, 0, None, None) == _lib.TF_EINVAL    # too many rows
+    assert lib.tf_qmm(p, p, p, p, big, 8, 64, 96, 64, 0, None, None) == _lib.TF_EINVAL      # K % 64
+    assert lib.tf_qmm(p, p, p, p, big, 8, 64, 64, 16, 0, None, None) == _lib.TF_EINVAL      # group
+    assert lib.tf_qmm(p + 2, p, p, p, big, 8, 64, 64, 64, 0, None, None) == _lib.TF_EALIGN
+    assert lib.tf_qmm(p, p, p, None, big, 8, 64, 64, 64, 0, None, None) == _lib.TF_ESCRATCH
+    assert lib.tf_qmm(p, p, p, p, 16, 8, 64, 64, 64, 0, None, None) == _lib.TF_ESCRATCH
 
 
 def test_k_schedule_is_a_function_of_shape_only():

@@ -39,7 +39,7 @@ def qmm(lib):
 def test_tile_roundtrip_keeps_every_bit(qmm, n, k, group):
     _, words, scales, biases = make(n, k, group, seed=n + k)
     q = qmm.tile_weight(words.cuda(), scales.cuda(), biases.cuda(), group)
-    assert q.tiled.numel() == (-(-n // 16)) * (k // 64) * (576 if group == 64 else 640)
+    assert q.tiled.numel() == (-(-n // 128)) * 8 * (k // 64) * (576 if group == 64 else 640)
     w2, s2, b2 = qmm.untile_weight(q)
     assert torch.equal(w2.cpu(), words) and torch.equal(s2.cpu().view(torch.int16), scales.view(torch.int16))
     assert torch.equal(b2.cpu().view(torch.int16), biases.view(torch.int16))
@@ -113,8 +113,8 @@ def test_given_group_sums_and_counters_left_zero(qmm):
     x, words, scales, biases = make(1024, 5120, 64, seed=4, rows=8)
     q = qmm.tile_weight(words.cuda(), scales.cuda(), biases.cuda(), 64)
     xc = x.cuda()
-    xs = qmm.group_sums(xc)
-    assert_same_bits(qmm.lane_matmul(xc, q, xs), qmm.lane_matmul(xc, q), "given xs")
+    packed = qmm.pack_rows(xc)
+    assert_same_bits(qmm.lane_matmul(packed, q), qmm.lane_matmul(xc, q), "rows packed by the caller")
     torch.cuda.synchronize()
     assert int(qmm.scratch_for(xc.device)[:16384].view(torch.int32).abs().sum()) == 0
 
