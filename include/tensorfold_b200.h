@@ -83,6 +83,131 @@ int tf_qmm_tile(const void* words, const void* scales, const void* biases, void*
 int tf_qmm_untile(const void* w_tiled, void* words, void* scales, void* biases, int N, int K, int group,
                   void* stream);
 
+
+/* ---- glue: the steps between two matmuls ----------------------------------------------------
+ * Each writes the next matmul's input in packed form (group sums included) when given a packed
+ * output, and/or plain row-major bf16. M is 1..128 rows. Strides are in elements. */
+
+/* h = bf16(x + r) where r is a bf16 row set (`residual`) or the rank-ordered sum, rounded once to
+ * bf16, of `nparts` fp32 partial row sets `partials + p * part_stride` (a row-parallel projection's
+ * per-rank outputs); y = bf16(h * rsqrt(mean(h^2) + eps) * weight). h_out receives h when a residual
+ * is given; y goes to y_rows [M, D] and/or y_packed. D a multiple of 256 up to 8192.
+ * Replaces: families/qwen3_5/cuda/glue.py:15-45 (add_rmsnorm), kernels/qwen/dense/v1/lane_glue.py:237-268
+ * (norm_xs), families/qwen3_5/cuda/distributed.py:267-289 (rank-ordered partial sum). */
+int tf_norm_xs(const void* x, const void* residual, const void* partials, int nparts, size_t part_stride,
+               const void* weight, void* h_out, void* y_rows, void* y_packed, int M, int D, int group, float eps,
+               void* stream);
+
+/* out = bf16(silu(gate) * up); gate and up are [M, I] views with row stride in_stride.
+ * Replaces: families/qwen3_5/cuda/glue.py:133-154 (swiglu), lane_glue.py:307-317 (mlp_act). */
+int tf_swiglu(const void* gate, const void* up, size_t in_stride, void* out_packed, void* out_rows, int M, int I,
+              int group, void* stream);
+
+/* out = bf16(silu(z) * (y * rsqrt(mean_head(y^2) + eps) * weight)) per value head; y [M, v_heads, dv]
+ * contiguous, z a [M, v_heads*dv] view with row stride z_stride, dv = 128.
+ * Replaces: families/qwen3_5/cuda/glue.py:108-130 (gated_norm), lane_glue.py:294-304 (gdn_post). */
+int tf_gated_norm(const void* y, const void* z, size_t z_stride, const void* weight, void* out_packed, void* out_rows,
+                  int M, int v_heads, int dv, int group, float eps, void* stream);
+
+/* out = bf16(o * sigmoid(gate)); o [M, heads, D] contiguous, gate = second half of each head's
+ * [q | gate] block in the rows `qg` (row stride qg_stride). D = 128 or 256.
+ * Replaces: families/qwen3_5/cuda/glue.py:206-226 (gate_mul), families/qwen4_exp/cuda/glue.py:369-387. */
+int tf_gate_mul(const void* o, const void* qg, size_t qg_stride, void* out_packed, void* out_rows, int M, int heads,
+                int head_dim, int group, void* stream);
+
+/* Per head: bf16(weight * x * rsqrt(mean(x^2) + eps)), then rotate-half RoPE at row_pos[row] over the
+ * first 2*rope_half dims with inv_freq[rope_half]; queries from the [q_h | gate_h] rows `qg`, keys from
+ * `k`; values are copied. Outputs contiguous q [M, heads, D], k and v [M, kv_heads, D].
+ * Replaces: families/qwen3_5/cuda/glue.py:157-203 (attn_prep), families/qwen4_exp/cuda/glue.py:298-366. */
+int tf_attn_prep(const void* qg, size_t qg_stride, const void* k, size_t k_stride, const void* v, size_t v_stride,
+                 const void* q_norm, const void* k_norm, const int* row_pos, const float* inv_freq, int rope_half,
+                 void* q_out, void* k_out, void* v_out, int M, int heads, int kv_heads, int head_dim, float eps,
+                 void* stream);
+
+/* Depthwise causal conv (4 taps) over each row's own chain [conv_state of its sequence (3 rows);
+ * the sequence's earlier window rows; the row], SiLU (rounded to bf16), split into q, k, v heads
+ * of 128; q and k RMS-normalised (eps 1e-6) and scaled by 1/dk and dk^-1/2; g = exp(-exp(a_log) *
+ * softplus(a + dt_bias)), beta = sigmoid(b). row_seq / row_idx give each packed row's sequence and
+ * its place in that sequence's window (a sequence's rows are consecutive, in chain order).
+ * conv_state [n_seqs, 3, C], conv_w [C, 4], C = (2*k_heads + v_heads) * 128.
+ * Replaces: families/qwen3_5/cuda/glue.py:48-105 (gdn_pre), lane_glue.py:271-291,
+ * families/qwen4_exp/cuda/gdn.cu:74-106 (conv + gates inside the chain kernel). */
+int tf_gdn_pre(const void* qkv, size_t qkv_stride, const void* conv_state, const void* conv_w, const int* row_seq,
+               const int* row_idx, const void* a, const void* b, size_t ab_stride, const float* a_log,
+               const float* dt_bias, void* q_out, void* k_out, void* v_out, float* g_out, float* beta_out, int M,
+               int k_heads, int v_heads, int dk, int dv, int taps, void* stream);
+
+/* x[row] = bf16(q * s + b) of embedding row ids[row]; table in the stored MLX layout
+ * (words [vocab, D/8], scales/biases [vocab, D/group]).
+ * Replaces: families/qwen3_5/cuda/glue.py:229-246 (embed), families/qwen4_exp/cuda/glue.py:34-59. */
+int tf_embed(const int* ids, const void* words, const void* scales, const void* biases, void* out, int M, int D,
+             int group, int vocab, void* stream);
+
+/* ---- gated-DeltaNet recurrence ---------------------------------------------------------------
+ * For each sequence (rows seq_start[s] .. seq_start[s+1]-1, in chain order), value head and value
+ * row:  S <- S*g;  mem = S.k;  delta = (v - mem)*beta;  S <- S + k*delta;  y = S.q  (fp32).
+ * state [n_seqs, v_heads, dv, 128] fp32 is only read; state_out (optional, same shape) receives
+ * the state after the window's last row. q, k [R, k_heads, 128], v, y [R, v_heads, dv] bf16;
+ * g, beta [R, v_heads] fp32. dk = 128, dv a multiple of 32.
+ * Replaces: families/qwen3_5/cuda/gdn_tree.cu:46-87 (tree_kernel, chain form),
+ * families/qwen4_exp/cuda/gdn.cu:49-152 (chain_kernel), kernels/qwen/dense/v1/lane_tree.py:132-182. */
+int tf_gdn_chain(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state,
+                 float* state_out, void* y, const int* seq_start, int n_seqs, int k_heads, int v_heads, int dk, int dv,
+                 void* stream);
+
+/* Commit: advance `state` in place over the first keep[s] rows of each sequence's window with the
+ * same statements as tf_gdn_chain, for `layers` layers in one launch (records and states of
+ * successive layers `*_stride` elements apart).
+ * Replaces: families/qwen3_5/cuda/gdn_tree.cu:89-154 (replay_kernel, replay_many_kernel),
+ * families/qwen4_exp/cuda/gdn.cu:154-181. */
+int tf_gdn_replay(const void* k, const void* v, const float* g, const float* beta, float* state, const int* seq_start,
+                  const int* keep, int n_seqs, int layers, long long rec_k_stride, long long rec_v_stride,
+                  long long rec_g_stride, long long state_stride, int k_heads, int v_heads, int dk, int dv,
+                  void* stream);
+
+/* Commit: conv_state[s] <- last 3 rows of [conv_state[s]; first keep[s] window rows of qkv].
+ * Replaces: families/qwen3_5/cuda/forward.py:226-236 (conv rows in commit). */
+int tf_conv_commit(const void* qkv, size_t qkv_stride, long long rec_qkv_stride, void* conv_state,
+                   long long state_stride, const int* seq_start, const int* keep, int n_seqs, int layers,
+                   int channels, void* stream);
+
+/* ---- lane attention over a paged KV cache ------------------------------------------------------
+ * Causal GQA for every window row of every sequence: row t of sequence s attends to the committed
+ * tokens 0..seq_lens[s]-1 (pages: k_pages / v_pages [page, kv_head, 16, D] bf16 through
+ * page_table [n_seqs, max_pages]) and to window rows 0..t of s (k_new / v_new [rows, kv_heads, D]).
+ * Keys are cut by absolute position into 512-key chunks of 64-key tiles; per-chunk (m, l, O)
+ * partials go to `scratch` (tf_attention_scratch_bytes) and are merged in chunk order.
+ * row_nkeys[row] = seq_lens[s] + t + 1. max_window = longest window, max_chunks >= ceil(max over s of
+ * (seq_lens[s] + window) / 512). q, out [rows, heads, D]; D = 128 or 256; heads/kv_heads <= 16.
+ * Replaces: families/qwen3_5/cuda/attention.py:152-201 (attention), families/qwen4_exp/cuda/attention.py:126-140,
+ * kernels/qwen/dense/v1/lane_attention.py:430-518 (lane_sdpa, lane_tree_sdpa; chains only). */
+size_t tf_attention_scratch_bytes(int rows, int heads, int head_dim, int max_chunks);
+int tf_lane_attention_paged(const void* q, const void* k_new, const void* v_new, const void* k_pages,
+                            const void* v_pages, const int* page_table, int max_pages, const int* seq_lens,
+                            const int* seq_start, const int* row_nkeys, void* out, void* scratch, size_t scratch_bytes,
+                            int rows, int n_seqs, int max_window, int max_chunks, int heads, int kv_heads, int head_dim,
+                            float scale, void* stream);
+
+/* Commit: copy the first keep[s] window rows of each sequence into its pages at positions
+ * seq_lens[s].., for `layers` layers in one launch.
+ * Replaces: families/qwen3_5/cuda/forward.py:237-251 (key/value rows in commit). */
+int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, void* k_pages, void* v_pages,
+                 long long pages_stride, const int* page_table, int max_pages, const int* seq_lens, const int* seq_start,
+                 const int* keep, int n_seqs, int layers, int kv_heads, int head_dim, void* stream);
+
+/* ---- exact top-k and keyed sampling --------------------------------------------------------------
+ * Each row's k largest bf16 logits (k <= 64), ordered by value descending then id ascending; ties at
+ * the cut go to the smallest ids. idx int32 [rows, k], val fp32 [rows, k].
+ * Replaces: engine/topk.py:20-146 (radix_topk, topk_rows). */
+int tf_topk_rows(const void* x, size_t row_stride, int rows, int vocab, int k, int* idx, float* val, void* stream);
+
+/* token = argmax over the kept candidates of val/temperature + Gumbel(splitmix64(seed, position, id));
+ * candidates (already ordered as tf_topk_rows writes them) are cut to top_k, then to the smallest
+ * prefix whose tempered probability reaches top_p. fp64 arithmetic.
+ * Replaces: engine/exact_sampling.py:57-109 (uniform_rows, choose_rows), engine/gpu_sampling.py:298-363. */
+int tf_sample_rows(const int* idx, const float* val, int width, const long long* positions, unsigned long long seed,
+                   double temperature, int top_k, double top_p, int* tokens, int rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

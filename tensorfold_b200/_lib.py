@@ -7,7 +7,7 @@ the boundary as raw device pointers; the stream is torch's current stream.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_size_t, c_void_p, c_float, c_longlong
+from ctypes import c_double, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
 from pathlib import Path
 
 import torch
@@ -32,6 +32,33 @@ SIGNATURES: dict[str, tuple] = {
     "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_norm_xs": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_float, c_void_p]),
+    "tf_swiglu": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_gated_norm": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_float, c_void_p]),
+    "tf_gate_mul": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_attn_prep": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "tf_gdn_pre": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_void_p]),
+    "tf_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_gdn_chain": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_gdn_replay": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                              c_longlong, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_conv_commit": (c_int, [c_void_p, c_size_t, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int,
+                               c_int, c_void_p]),
+    "tf_attention_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tf_lane_attention_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_float, c_void_p]),
+    "tf_kv_commit": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "tf_sample_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_ulonglong, c_double, c_int, c_double, c_void_p,
+                               c_int, c_void_p]),
 }
 
 _lib = None

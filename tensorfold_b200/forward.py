@@ -1,0 +1,327 @@
+"""The verify forward of the dense hybrid decoder (gated-DeltaNet layers with a full-attention layer
+every ``interval``-th), over the ragged chain windows of many sequences, and its commit.
+
+Mirror of the reference's ``tree_forward`` / ``commit`` / ``State``
+(``families/qwen3_5/cuda/forward.py:78-252``; Metal ``kernels/qwen/dense/v1/lane_tree.py:276-392``):
+the committed state is read-only until ``commit``; a serial decode step is the same forward with a
+one-row window followed by a one-row commit, so a window row has the bits of the serial step at its
+position. Differences from the reference, all inside its contract: windows are chains (no trees);
+many sequences ride in one forward as packed rows; the KV cache is paged (16-token pages); the
+projections that share an input are stacked ([qkv|z|b|a], [q|k|v], [gate|up]).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import torch
+
+from . import lane_attention as LA
+from . import lane_gdn, lane_glue
+from .lane_qmm import MAX_ROWS, QWeight, lane_matmul, new_packed, tile_weight
+
+
+@dataclass
+class Config:
+    """The fields of the reference's ``Config`` (``families/qwen3_5/cuda/weights.py:38-59``) the forward uses."""
+
+    hidden: int
+    intermediate: int
+    layers: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    vocab: int
+    k_heads: int
+    v_heads: int
+    dk: int = 128
+    dv: int = 128
+    conv_kernel: int = 4
+    interval: int = 4
+    eps: float = 1e-6
+    rope_dims: int = 0
+    rope_theta: float = 1e7
+    group: int = 64
+
+    def __post_init__(self):
+        if not self.rope_dims:
+            self.rope_dims = self.head_dim // 4
+        if self.dk != 128 or self.dv != 128 or self.conv_kernel != 4:
+            raise ValueError("this build supports GDN heads of 128 and a 4-tap conv")
+
+    def is_linear(self, layer: int) -> bool:
+        return (layer + 1) % self.interval != 0
+
+    @property
+    def conv_channels(self) -> int:
+        return (2 * self.k_heads + self.v_heads) * 128
+
+    def inv_freq(self) -> torch.Tensor:
+        half = self.rope_dims // 2
+        return (self.rope_theta ** (-torch.arange(0, half, dtype=torch.float64) / half)).to(torch.float32)
+
+
+@dataclass
+class LayerWeights:
+    linear: bool
+    input_norm: torch.Tensor
+    post_norm: torch.Tensor
+    in_proj: QWeight                  # GDN: [qkv | z | b | a]; attention: [q (with gates) | k | v]
+    out_proj: QWeight
+    gate_up: QWeight                  # [gate | up]
+    down: QWeight
+    conv: torch.Tensor | None = None
+    A_log: torch.Tensor | None = None
+    dt_bias: torch.Tensor | None = None
+    norm: torch.Tensor | None = None
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+
+
+@dataclass
+class Weights:
+    config: Config
+    embed: tuple                      # (words, scales, biases) in the stored layout
+    layers: list
+    norm: torch.Tensor
+    head: QWeight
+    inv_freq: torch.Tensor
+
+    def nbytes(self) -> int:
+        """Bytes of 4-bit projection weights one forward streams (the weight-bytes roofline numerator)."""
+
+        total = self.head.nbytes()
+        for l in self.layers:
+            total += l.in_proj.nbytes() + l.out_proj.nbytes() + l.gate_up.nbytes() + l.down.nbytes()
+        return total
+
+
+def _stack(parts, device, group) -> QWeight:
+    """Several projections of the same input as one: stored-layout rows concatenated in order, then tiled
+    (reference: ``qmm_fast.stack``)."""
+
+    words = torch.cat([p.words for p in parts]).to(device)
+    scales = torch.cat([p.scales for p in parts]).to(device)
+    biases = torch.cat([p.biases for p in parts]).to(device)
+    return tile_weight(words.contiguous(), scales.contiguous(), biases.contiguous(), group)
+
+
+def load_weights(model: dict, device="cuda") -> Weights:
+    """Build device weights from stored-layout arrays: ``model`` maps names to objects with ``words``,
+    ``scales``, ``biases`` (4-bit projections) or to tensors, as ``families/qwen3_5/cuda/weights.py``
+    reads them from a checkpoint: per layer ``qkv z b a out conv A_log dt_bias norm`` or ``q k v o q_norm
+    k_norm``, plus ``input_norm post_norm gate up down``; top level ``embed norm head config``."""
+
+    c = model["config"]
+    cfg = Config(**{f: getattr(c, f) for f in Config.__dataclass_fields__ if hasattr(c, f)}) if not isinstance(c, Config) else c
+    g = cfg.group
+    layers = []
+    for src in model["layers"]:
+        def dev(name):
+            return src[name].to(device).contiguous()
+        if src["linear"]:
+            lw = LayerWeights(True, dev("input_norm"), dev("post_norm"), _stack([src["qkv"], src["z"], src["b"], src["a"]], device, g),
+                              _stack([src["out"]], device, g), _stack([src["gate"], src["up"]], device, g),
+                              _stack([src["down"]], device, g), conv=dev("conv"), A_log=dev("A_log").float(),
+                              dt_bias=dev("dt_bias").float(), norm=dev("norm"))
+        else:
+            lw = LayerWeights(False, dev("input_norm"), dev("post_norm"), _stack([src["q"], src["k"], src["v"]], device, g),
+                              _stack([src["o"]], device, g), _stack([src["gate"], src["up"]], device, g),
+                              _stack([src["down"]], device, g), q_norm=dev("q_norm"), k_norm=dev("k_norm"))
+        layers.append(lw)
+    e = model["embed"]
+    embed = (e.words.to(device).contiguous(), e.scales.to(device).contiguous(), e.biases.to(device).contiguous())
+    return Weights(cfg, embed, layers, model["norm"].to(device).contiguous(), _stack([model["head"]], device, g),
+                   cfg.inv_freq().to(device))
+
+
+class State:
+    """Committed state of ``n_seqs`` sequences: paged K/V for the attention layers, conv tail and fp32
+    recurrent state for the GDN layers, and each sequence's committed length. Read-only during a
+    forward; only ``commit`` writes it (reference: ``forward.State``)."""
+
+    def __init__(self, w: Weights, n_seqs: int, max_context: int, device=None, num_pages: int | None = None):
+        c = w.config
+        device = device or w.norm.device
+        self.n_seqs = n_seqs
+        self.lens = [0] * n_seqs
+        self.seq_lens = torch.zeros(n_seqs, dtype=torch.int32, device=device)
+        self.gdn_layers = [i for i, l in enumerate(w.layers) if l.linear]
+        self.att_layers = [i for i, l in enumerate(w.layers) if not l.linear]
+        pages_per_seq = -(-(max_context + MAX_ROWS) // LA.PAGE)
+        self.kv = LA.PagedKV(len(self.att_layers), n_seqs, num_pages or n_seqs * pages_per_seq, c.kv_heads, c.head_dim,
+                             pages_per_seq, device)
+        ng = max(len(self.gdn_layers), 1)
+        self.conv = torch.zeros((ng, n_seqs, c.conv_kernel - 1, c.conv_channels), dtype=torch.bfloat16, device=device)
+        self.rec = torch.zeros((ng, n_seqs, c.v_heads, c.dv, c.dk), dtype=torch.float32, device=device)
+
+    def sync_lens(self) -> None:
+        self.seq_lens.copy_(torch.tensor(self.lens, dtype=torch.int32), non_blocking=True)
+
+
+@dataclass
+class Batch:
+    """Row bookkeeping of one forward: which sequence and which place in its chain each packed row has."""
+
+    widths: list
+    rows: int
+    seq_start: torch.Tensor
+    row_seq: torch.Tensor
+    row_idx: torch.Tensor
+    row_pos: torch.Tensor
+    row_nkeys: torch.Tensor
+    max_window: int
+    max_chunks: int
+
+
+def make_batch(st: State, widths: Sequence[int], device, max_chunks: int | None = None) -> Batch:
+    widths = [int(x) for x in widths]
+    if len(widths) != st.n_seqs or any(x < 0 for x in widths) or sum(widths) < 1:
+        raise ValueError("one window width per sequence (0 = idle), at least one row in all")
+    rows = sum(widths)
+    if rows > MAX_ROWS:
+        raise ValueError(f"a forward takes at most {MAX_ROWS} packed rows, got {rows}")
+    starts, seq, idx, pos, nk = [0], [], [], [], []
+    for s, wd in enumerate(widths):
+        starts.append(starts[-1] + wd)
+        for t in range(wd):
+            seq.append(s); idx.append(t); pos.append(st.lens[s] + t); nk.append(st.lens[s] + t + 1)
+    need = max(-(-(st.lens[s] + wd) // LA.CHUNK) for s, wd in enumerate(widths))
+    def i32(v):
+        return torch.tensor(v, dtype=torch.int32).to(device, non_blocking=True)
+    return Batch(widths, rows, i32(starts), i32(seq), i32(idx), i32(pos), i32(nk), max(widths), max(max_chunks or 0, need, 1))
+
+
+@dataclass
+class Record:
+    """What a forward leaves for ``commit``: per GDN layer the window's k, v, g, beta and stacked
+    projection rows (qkv for the conv tail), per attention layer the window's K/V rows."""
+
+    batch: Batch
+    gdn_k: torch.Tensor
+    gdn_v: torch.Tensor
+    gdn_g: torch.Tensor
+    gdn_beta: torch.Tensor
+    gdn_in: torch.Tensor
+    att_k: torch.Tensor
+    att_v: torch.Tensor
+
+
+@torch.no_grad()
+def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_logits: bool = True,
+                 max_chunks: int | None = None, batch: Batch | None = None):
+    """Logits (rows, vocab) bf16 for the window rows, and the record ``commit`` needs.
+
+    ``windows``: one window width per sequence of ``st`` (packed rows are each sequence's chain in
+    order), or, for a single sequence, the reference's ``parents`` list of a chain ([-1, 0, 1, ...]).
+    The state is untouched. ``full_logits=False`` returns the final-normed hidden rows instead.
+    """
+
+    c = w.config
+    dev = w.norm.device
+    if batch is None:
+        windows = list(windows)
+        if st.n_seqs == 1 and windows and windows[0] == -1:
+            windows = [lane_gdn.chain_parents(windows)]
+        for s, wd in enumerate(windows):
+            if wd and st.kv.reserve(s, st.lens[s] + wd):
+                st.kv.sync_table()
+        st.sync_lens()
+        batch = make_batch(st, windows, dev, max_chunks)
+    b = batch
+    R = b.rows
+    if tokens.shape != (R,) or tokens.dtype not in (torch.int32, torch.int64) or tokens.device != dev:
+        raise ValueError("tokens must be a 1-D int tensor on the weights' device, one per window row")
+    g = c.group
+    kd, vd = c.k_heads * c.dk, c.v_heads * c.dv
+    ng, na = max(len(st.gdn_layers), 1), max(len(st.att_layers), 1)
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    rec = Record(b, torch.empty((ng, R, c.k_heads, c.dk), **bf), torch.empty((ng, R, c.v_heads, c.dv), **bf),
+                 torch.empty((ng, R, c.v_heads), dtype=torch.float32, device=dev),
+                 torch.empty((ng, R, c.v_heads), dtype=torch.float32, device=dev),
+                 torch.empty((ng, R, 2 * kd + 2 * vd + 2 * c.v_heads), **bf),
+                 torch.empty((na, R, c.kv_heads, c.head_dim), **bf), torch.empty((na, R, c.kv_heads, c.head_dim), **bf))
+    q_gdn = torch.empty((R, c.k_heads, c.dk), **bf)
+    y_gdn = torch.empty((R, c.v_heads, c.dv), **bf)
+    q_att = torch.empty((R, c.heads, c.head_dim), **bf)
+    o_att = torch.empty((R, c.heads, c.head_dim), **bf)
+    att_in = torch.empty((R, c.heads * 2 * c.head_dim + 2 * c.kv_heads * c.head_dim), **bf)
+    mlp_in = torch.empty((R, 2 * c.intermediate), **bf)
+    scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
+    scale = c.head_dim ** -0.5
+
+    x = lane_glue.embed(tokens.to(torch.int32), *w.embed, c.hidden, g)
+    pending = None
+    gi = ai = 0
+    for layer in w.layers:
+        x, h = lane_glue.norm_xs(x, pending, layer.input_norm, c.eps, group=g)
+        if layer.linear:
+            proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi])
+            qkv, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
+            bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + c.v_heads], proj[:, 2 * kd + 2 * vd + c.v_heads:]
+            lane_glue.gdn_pre(qkv, st.conv[gi], layer.conv, b.row_seq, b.row_idx, aa, bb, layer.A_log, layer.dt_bias,
+                              nk=c.k_heads, nv=c.v_heads, out=(q_gdn, rec.gdn_k[gi], rec.gdn_v[gi], rec.gdn_g[gi], rec.gdn_beta[gi]))
+            lane_gdn.gated_delta_chain(q_gdn, rec.gdn_k[gi], rec.gdn_v[gi], rec.gdn_g[gi], rec.gdn_beta[gi], st.rec[gi],
+                                       b.seq_start, out=y_gdn)
+            mixed = lane_glue.gdn_post(y_gdn, z, layer.norm, c.eps, group=g)
+            gi += 1
+        else:
+            proj = lane_matmul(h, layer.in_proj, out=att_in)
+            nq = c.heads * 2 * c.head_dim
+            nkv = c.kv_heads * c.head_dim
+            lane_glue.attn_prep(proj[:, :nq], proj[:, nq:nq + nkv], proj[:, nq + nkv:], layer.q_norm, layer.k_norm, b.row_pos,
+                                w.inv_freq, c.eps, heads=c.heads, kv_heads=c.kv_heads, head_dim=c.head_dim,
+                                out=(q_att, rec.att_k[ai], rec.att_v[ai]))
+            LA.lane_attention(q_att, rec.att_k[ai], rec.att_v[ai], st.kv.k[ai], st.kv.v[ai], st.kv.table, st.seq_lens,
+                              b.seq_start, b.row_nkeys, scale=scale, max_window=b.max_window, max_chunks=b.max_chunks,
+                              scratch=scratch, out=o_att)
+            mixed = lane_glue.gate_mul(o_att, proj[:, :nq], heads=c.heads, head_dim=c.head_dim, group=g)
+            ai += 1
+        r = lane_matmul(mixed, layer.out_proj)
+        x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g)
+        gu = lane_matmul(h, layer.gate_up, out=mlp_in)
+        act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)
+        pending = lane_matmul(act, layer.down)
+    if not full_logits:
+        _, hrows = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, rows_out=True, packed_out=False)
+        return hrows, rec
+    _, h = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g)
+    return lane_matmul(h, w.head), rec
+
+
+@torch.no_grad()
+def commit(st: State, record: Record, keep: Sequence[int]) -> None:
+    """Keep the first ``keep[s]`` rows of every sequence's window: K/V rows go into the pages, the GDN
+    state is replayed over them and the conv tail shifted, for all layers in three launches
+    (reference: ``forward.commit`` with an accepted path)."""
+
+    b = record.batch
+    keep = [int(k) for k in keep]
+    if len(keep) != st.n_seqs or any(k < 0 or k > wd for k, wd in zip(keep, b.widths)):
+        raise ValueError("keep must give, per sequence, a row count within its window")
+    dev = st.seq_lens.device
+    keep_t = torch.tensor(keep, dtype=torch.int32).to(dev, non_blocking=True)
+    if st.gdn_layers:
+        lane_gdn.replay(record.gdn_k, record.gdn_v, record.gdn_g, record.gdn_beta, st.rec, b.seq_start, keep_t)
+        lane_gdn.conv_commit(record.gdn_in, st.conv, b.seq_start, keep_t, st.conv.shape[-1])
+    if st.att_layers:
+        LA.kv_commit(record.att_k, record.att_v, st.kv, st.seq_lens, b.seq_start, keep_t)
+    for s, k in enumerate(keep):
+        st.lens[s] += k
+    st.sync_lens()
+
+
+def accept_path(drafted: Sequence[int], verified: Sequence[int]) -> int:
+    """Rows of a chain window to keep: row 0 is always kept (its input token was already decided);
+    row t+1 is kept while the token verified at row t equals the token drafted as row t+1's input
+    (reference: ``lane_tree.accept_path`` for a chain)."""
+
+    n = 1
+    while n < len(drafted) and int(drafted[n]) == int(verified[n - 1]):
+        n += 1
+    return n
+
+
+__all__ = ["Batch", "Config", "LayerWeights", "Record", "State", "Weights", "accept_path", "commit", "load_weights",
+           "make_batch", "tree_forward"]

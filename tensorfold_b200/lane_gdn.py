@@ -1,0 +1,106 @@
+"""Gated-DeltaNet recurrence for verify windows, and its commit.
+
+Host-side mirror of the reference's ``gated_delta_tree`` / ``replay_path``
+(``kernels/qwen/dense/v1/lane_tree.py:132-182``), ``tree / replay / replay_many``
+(``families/qwen3_5/cuda/gdn_tree.py:29-53``) and the batched-sequence step of ``LaneGDNCache``
+(``kernels/qwen/dense/v1/lane_gdn.py:377-450``), for chain windows of many sequences at once. The
+committed state is read-only during a forward; ``replay`` advances it over the accepted rows with
+the kernel's own arithmetic, so it equals the state serial one-row steps would have left.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def chain_parents(parents) -> int:
+    """Validate a reference-style ``parents`` list as one chain ([-1, 0, 1, ...]); returns its length."""
+
+    parents = [int(p) for p in parents]
+    if not parents or parents[0] != -1:
+        raise ValueError("a verify window needs a root at row zero")
+    if any(p != i - 1 for i, p in enumerate(parents)):
+        raise ValueError("this build verifies chain windows only (parents must be [-1, 0, 1, ...])")
+    return len(parents)
+
+
+def gated_delta_chain(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                      state: torch.Tensor, seq_start: torch.Tensor, *, state_out: torch.Tensor | None = None,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """y (R, Hv, Dv) bf16 for the packed window rows of every sequence, from the untouched ``state``.
+
+    q, k (R, Hk, 128) bf16; v (R, Hv, Dv) bf16; g, beta (R, Hv) fp32; state (S, Hv, Dv, 128) fp32;
+    ``seq_start`` int32 (S+1,) first packed row of each sequence. ``state_out`` (optional) receives
+    the state after each sequence's last row.
+    """
+
+    _lib.need_cuda(q, k, v, g, beta, state, seq_start)
+    r, hk, dk = q.shape
+    hv, dv = v.shape[1], v.shape[2]
+    s = state.shape[0]
+    if (q.dtype != torch.bfloat16 or k.shape != q.shape or v.shape[0] != r or g.shape != (r, hv) or beta.shape != g.shape
+            or g.dtype != torch.float32 or state.dtype != torch.float32 or state.shape != (s, hv, dv, dk)
+            or seq_start.dtype != torch.int32 or seq_start.shape != (s + 1,)):
+        raise ValueError("gated_delta_chain: inconsistent shapes or dtypes")
+    for t in (q, k, v, g, beta, state):
+        if not t.is_contiguous():
+            raise ValueError("gated_delta_chain: tensors must be contiguous")
+    if out is None:
+        out = torch.empty((r, hv, dv), dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().tf_gdn_chain(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                                            state.data_ptr(), _lib.ptr(state_out), out.data_ptr(), seq_start.data_ptr(),
+                                            s, hk, hv, dk, dv, _lib.stream()), "gated_delta_chain")
+    return out
+
+
+def gated_delta_tree(q, k, v, g, beta, state, parents) -> torch.Tensor:
+    """Reference signature for one sequence: ``parents`` must describe a chain."""
+
+    n = chain_parents(parents if not torch.is_tensor(parents) else parents.tolist())
+    seq_start = torch.tensor([0, n], dtype=torch.int32, device=q.device)
+    return gated_delta_chain(q, k, v, g, beta, state.reshape(1, *state.shape[-3:]), seq_start)
+
+
+def replay(k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+           seq_start: torch.Tensor, keep: torch.Tensor) -> None:
+    """Advance ``state`` in place over the first ``keep[s]`` window rows of every sequence, for one layer
+    (k (R, Hk, 128) ...) or for all layers in one launch (k (Layers, R, Hk, 128), state (Layers, S, ...))."""
+
+    _lib.need_cuda(k, v, g, beta, state, seq_start, keep)
+    many = k.dim() == 4
+    layers = k.shape[0] if many else 1
+    r, hk, dk = k.shape[-3:]
+    hv, dv = v.shape[-2:]
+    s = state.shape[-4]
+    if keep.dtype != torch.int32 or keep.shape != (s,) or seq_start.shape != (s + 1,) or state.dtype != torch.float32:
+        raise ValueError("replay: keep and seq_start must be int32 per sequence, state fp32")
+    for t in (k, v, g, beta, state):
+        if not t.is_contiguous():
+            raise ValueError("replay: tensors must be contiguous")
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.load().tf_gdn_replay(k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(),
+                                             seq_start.data_ptr(), keep.data_ptr(), s, layers, r * hk * dk, r * hv * dv,
+                                             r * hv, s * hv * dv * dk, hk, hv, dk, dv, _lib.stream()), "replay")
+
+
+replay_path = replay
+
+
+def conv_commit(qkv: torch.Tensor, conv_state: torch.Tensor, seq_start: torch.Tensor, keep: torch.Tensor, channels: int) -> None:
+    """conv_state[s] <- last 3 rows of [conv_state[s]; the first keep[s] window rows], in place.
+    ``qkv`` (R, >=C) row views or (Layers, R, >=C); conv_state (S, 3, C) or (Layers, S, 3, C)."""
+
+    many = qkv.dim() == 3
+    layers = qkv.shape[0] if many else 1
+    s = conv_state.shape[-3]
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.load().tf_conv_commit(qkv.data_ptr(), qkv.stride(-2), qkv.stride(0) if many else 0,
+                                              conv_state.data_ptr(), conv_state.stride(0) if many else 0,
+                                              seq_start.data_ptr(), keep.data_ptr(), s, layers, channels, _lib.stream()),
+                   "conv_commit")
+
+
+__all__ = ["chain_parents", "conv_commit", "gated_delta_chain", "gated_delta_tree", "replay", "replay_path"]
