@@ -1,0 +1,322 @@
+"""Lane-verify throughput of the 27B-class 4-bit dense hybrid decoder on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--seqs S] [--ctx C] [--width 8] [--impl ours|reference]
+
+A step is one verify forward (all 64 layers + head + token choice) over S sequences x W drafted rows
+with C committed tokens of context each; weights are random 4-bit group-64 of the 27B-class
+architecture (BASELINE config 3), prompts random token ids, the context built by real prefill through
+the same kernels. Prints ONE JSON line (rank 0). With N > 1 the model is tensor-parallel over N ranks
+(launch under torchrun). ``--impl reference`` times the CPU restatement of the reference arithmetic
+(``oracle/``) on the host cores for the same workload, on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v == "Active":
+                    reasons.add(name)
+        mx = max((int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference(args, rows: int):
+    """The reference arithmetic on the host cores (oracle port): one GDN layer and one attention layer of
+    the 27B-class shapes over the step's rows, scaled to 48 + 16 layers + head by weight count."""
+
+    import torch
+
+    from oracle import lane_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = O.Config(hidden=5120, intermediate=17408, layers=4, heads=24, kv_heads=4, head_dim=256, vocab=256, k_heads=16,
+                   v_heads=32, dk=128, dv=128, rope_dims=64)
+    gen = torch.Generator().manual_seed(0)
+    c = cfg
+    kd, vd = c.k_heads * c.dk, c.v_heads * c.dv
+    x = torch.randn((rows, c.hidden), generator=gen).to(torch.bfloat16)
+    norm = torch.ones(c.hidden, dtype=torch.bfloat16)
+
+    def lin(inp, n, k):
+        q = O.random_q4(gen, n, k, 64)
+        return O.qmm(inp, q.words, q.scales, q.biases, 64)
+
+    def mlp(h):
+        act = O.swiglu(lin(h, c.intermediate, c.hidden), lin(h, c.intermediate, c.hidden))
+        return lin(act, c.hidden, c.intermediate)
+
+    t0 = time.perf_counter()
+    _, h = O.add_rmsnorm(x, None, norm, c.eps)
+    qkv, z, b, a = lin(h, 2 * kd + vd, c.hidden), lin(h, vd, c.hidden), lin(h, c.v_heads, c.hidden), lin(h, c.v_heads, c.hidden)
+    q, k, v, g, beta = O.gdn_pre(qkv, torch.zeros((3, 2 * kd + vd), dtype=torch.bfloat16), torch.ones((2 * kd + vd, 4), dtype=torch.bfloat16),
+                                 a, b, torch.zeros(c.v_heads), torch.zeros(c.v_heads), kh=c.k_heads, vh=c.v_heads, dk=128, dv=128)
+    per_seq = args.width
+    ys = []
+    for s0 in range(0, rows, per_seq):
+        y, _ = O.gdn_recurrence(q[s0:s0 + per_seq], k[s0:s0 + per_seq], v[s0:s0 + per_seq], g[s0:s0 + per_seq], beta[s0:s0 + per_seq],
+                                torch.zeros((c.v_heads, 128, 128)))
+        ys.append(y)
+    out = O.gated_norm(torch.cat(ys), z.reshape(rows, c.v_heads, 128), torch.ones(128, dtype=torch.bfloat16), c.eps)
+    x1 = (x.float() + lin(out, c.hidden, vd).float()).to(torch.bfloat16)
+    _, h = O.add_rmsnorm(x1, None, norm, c.eps)
+    x1 = (x1.float() + mlp(h).float()).to(torch.bfloat16)
+    t_gdn = time.perf_counter() - t0
+
+    t0 = time.perf_counter()
+    _, h = O.add_rmsnorm(x1, None, norm, c.eps)
+    qg, kk, vv = lin(h, c.heads * 2 * c.head_dim, c.hidden), lin(h, c.kv_heads * c.head_dim, c.hidden), lin(h, c.kv_heads * c.head_dim, c.hidden)
+    pos = torch.arange(rows) % per_seq + 256
+    qh, kh_ = O.attn_prep(qg, kk, torch.ones(c.head_dim, dtype=torch.bfloat16), torch.ones(c.head_dim, dtype=torch.bfloat16), pos,
+                          cfg.inv_freq(), c.eps, heads=c.heads, kv_heads=c.kv_heads, head_dim=c.head_dim)
+    ctx = 256                                                   # a short context: the sample is bounded by the projections
+    kc = torch.randn((ctx + per_seq, c.kv_heads, c.head_dim), generator=gen).to(torch.bfloat16)
+    os_ = []
+    for s0 in range(0, rows, per_seq):
+        os_.append(O.attention(qh[s0:s0 + per_seq], kc, kc, torch.arange(per_seq) + ctx + 1, c.head_dim ** -0.5))
+    o = O.gate_mul(torch.cat(os_), qg, heads=c.heads, head_dim=c.head_dim)
+    x2 = (x1.float() + lin(o, c.hidden, c.heads * c.head_dim).float()).to(torch.bfloat16)
+    _, h = O.add_rmsnorm(x2, None, norm, c.eps)
+    x2 = (x2.float() + mlp(h).float()).to(torch.bfloat16)
+    t_att = time.perf_counter() - t0
+    layer_params = 3 * c.intermediate * c.hidden + (2 * kd + 2 * vd + 2 * c.v_heads + vd) * c.hidden
+    t_head = t_gdn * (248320 * c.hidden) / layer_params
+    total = 48 * t_gdn + 16 * t_att + t_head
+    return {"value": rows / total, "unit": "rows/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 GDN layer ({t_gdn:.1f} s) + 1 attention layer at 256 keys ({t_att:.1f} s) of the 27B-class shapes over "
+                      f"{rows} rows, scaled to 48 + 16 layers + head by weight count"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--seqs", type=int, default=16)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--width", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rows = args.seqs * args.width
+    workload = (f"dense hybrid 27B-class 4-bit g64 verify forward: {args.layers} layers (3 gated-DeltaNet : 1 GQA), hidden 5120, "
+                f"MLP 17408, vocab 248320; {args.seqs} sequences x W={args.width} rows, context {args.ctx}")
+    config = {"workload": workload, "seqs": args.seqs, "width": args.width, "context": args.ctx, "parallelism": f"tp{world}",
+              "l2": "weights (13.6 GB per forward) exceed the 126 MB L2; no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base = cpu_reference(args, rows)
+        print(json.dumps({"metric": "lane-verify rows/sec", "value": base["value"], "unit": "rows/s", "n_gpus": args.gpus,
+                          "steps": 1, "warmup": 0, "ms_per_step": 1000.0 * rows / base["value"], "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+                          "config": config, "cpu_baseline": base,
+                          "e2e": {"value": base["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+
+    from tensorfold_b200 import _lib, build, forward as F, lane_qmm, runner, synthetic
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the lane kernels have no CPU path")
+    build.build()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    tp = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from tensorfold_b200 import distributed
+
+        dist.init_process_group("nccl", device_id=dev)
+        tp = distributed.RankGroup()
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
+
+    spec = dict(synthetic.DENSE_27B, layers=args.layers)
+    cfg = F.Config(**spec)
+    w = synthetic.random_weights(cfg, seed=2, device=dev, rank=rank, world=world)
+    st = F.State(w, args.seqs, args.ctx + 2 * args.width, dev)
+    run = runner.LaneRunner(w, st, [args.width] * args.seqs, max_context=args.ctx + args.width, tp=tp)
+    run.capture()
+
+    # ---- context: real prefill, W rows per sequence per replay, through the captured step ----
+    gen = torch.Generator(device=dev).manual_seed(7)
+    full = [args.width] * args.seqs
+    while st.lens[0] + args.width <= args.ctx:
+        run.tokens.copy_(torch.randint(0, cfg.vocab, (rows,), generator=gen, device=dev, dtype=torch.int32))
+        run.step_device()
+        run.commit(full)
+    if st.lens[0] < args.ctx:                       # context not a multiple of W: a last partial commit
+        run.tokens.copy_(torch.randint(0, cfg.vocab, (rows,), generator=gen, device=dev, dtype=torch.int32))
+        run.step_device()
+        run.commit([args.ctx - st.lens[0]] * args.seqs)
+    torch.cuda.synchronize(dev)
+    _lib.status(dev).raise_if_set()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    run.tokens.copy_(torch.randint(0, cfg.vocab, (rows,), generator=gen, device=dev, dtype=torch.int32))
+    for _ in range(max(args.warmup, 3)):
+        run.step_device()
+    # spin the clocks up: short bursts right after idle run at low clocks
+    t_end = time.time() + 0.5
+    while time.time() < t_end:
+        run.step_device()
+        torch.cuda.synchronize(dev)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            run.step_device()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    value = args.steps * rows / (ms / 1000.0)
+
+    # ---- end to end through the public call: host tokens in, chosen tokens out, every step ----
+    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run.step(host_tokens)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    # ---- dominant kernel: the lane matmul, every launch of one forward replayed alone ----
+    mats = []
+    for layer in w.layers:
+        mats += [layer.in_proj, layer.out_proj, layer.gate_up, layer.down]
+    mats.append(w.head)
+    packs = {}
+    for q in mats:
+        if q.k not in packs:
+            packs[q.k] = lane_qmm.pack_rows(torch.randn((rows, q.k), device=dev).to(torch.bfloat16), cfg.group)
+    outs = {q.n: torch.empty((rows, q.n), dtype=torch.bfloat16, device=dev) for q in mats}
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        for q in mats[:5]:
+            lane_qmm.lane_matmul(packs[q.k], q, out=outs[q.n])
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for q in mats:
+                lane_qmm.lane_matmul(packs[q.k], q, out=outs[q.n])
+    torch.cuda.synchronize(dev)
+    g.replay()
+    torch.cuda.synchronize(dev)
+    q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    q0.record()
+    for _ in range(reps):
+        g.replay()
+    q1.record()
+    torch.cuda.synchronize(dev)
+    qmm_ms = q0.elapsed_time(q1) / reps
+
+    def alg_bytes(q):
+        kg = q.k // q.group
+        return q.n * q.k // 2 + q.n * kg * 4 + rows * q.k * 2 + rows * kg * 4 + rows * q.n * 2
+    total_bytes = sum(alg_bytes(q) for q in mats)
+    peak, peak_kind = peaks()
+    achieved = total_bytes / (qmm_ms / 1000.0) / 1e9
+    weight_bytes = sum(q.n * q.k // 2 + q.n * (q.k // q.group) * 4 for q in mats)
+    _lib.status(dev).raise_if_set()
+    if rank != 0:
+        return
+    line = {
+        "metric": "lane-verify rows/sec", "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+        "clocks": clk.summary(),
+        "e2e": {"value": args.steps * rows / e2e_s, "unit": "rows/s", "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * 4},
+        "gpu_launches": run.launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
+                     "kernel": "qmm_kernel (4-bit lane matmul)", "launches_per_step": len(mats),
+                     "avg_launch_us": 1000.0 * qmm_ms / len(mats), "algorithmic_bytes_per_launch": total_bytes / len(mats),
+                     "traffic": 0.995 * total_bytes / len(mats),
+                     "traffic_note": "dram bytes of one ncu capture (17408x5120, 8 rows: 50.26 MB read for 50.50 MB algorithmic), scaled by units"},
+        "forward": {"weight_bytes_per_step": weight_bytes, "weight_roofline_ms": weight_bytes / (peak * 1e6),
+                    "frac_of_weight_roofline": (weight_bytes / (peak * 1e6)) / (ms / args.steps),
+                    "qmm_ms_per_step": qmm_ms, "qmm_share": qmm_ms / (ms / args.steps)},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_reference(args, rows)
+    print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,28 @@ SIGNATURES: dict[str, tuple] = {
 }
 
 _lib = None
+_launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
+_NO_LAUNCH = {"tf_version", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
+              "tf_attention_scratch_bytes"}
+
+
+def launch_count() -> int:
+    return _launches
+
+
+class _Counted:
+    """A bound entry point that counts successful kernel launches (tf_lane_attention_paged queues two)."""
+
+    def __init__(self, fn, n):
+        self.fn, self.n = fn, n
+
+    def __call__(self, *args):
+        global _launches
+        rc = self.fn(*args)
+        if rc == 0:
+            _launches += self.n
+        return rc
+
 
 
 def load() -> ctypes.CDLL:
@@ -73,11 +95,17 @@ def load() -> ctypes.CDLL:
             raise RuntimeError(f"{LIB_PATH} is missing: run `python -m tensorfold_b200.build` "
                                "(there is no CPU or PyTorch fallback for the lane kernels)")
         lib = ctypes.CDLL(str(LIB_PATH))
+        class Bound:
+            pass
+
+        bound = Bound()
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
-        _lib = lib
+            setattr(bound, name, fn if name in _NO_LAUNCH else _Counted(fn, 2 if name == "tf_lane_attention_paged" else 1))
+        bound.cdll = lib
+        _lib = bound
     return _lib
 
 

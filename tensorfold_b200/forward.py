@@ -175,6 +175,27 @@ class Batch:
     max_chunks: int
 
 
+def _batch_lists(st: State, widths):
+    starts, seq, idx, pos, nk = [0], [], [], [], []
+    for s, wd in enumerate(widths):
+        starts.append(starts[-1] + wd)
+        for t in range(wd):
+            seq.append(s); idx.append(t); pos.append(st.lens[s] + t); nk.append(st.lens[s] + t + 1)
+    return starts, seq, idx, pos, nk
+
+
+def refresh_batch(b: Batch, st: State) -> None:
+    """Rewrite a batch's position tensors in place from the state's current lengths (same widths):
+    what a captured CUDA graph needs before each replay."""
+
+    _, _, _, pos, nk = _batch_lists(st, b.widths)
+    need = max(-(-(st.lens[s] + wd) // LA.CHUNK) for s, wd in enumerate(b.widths))
+    if need > b.max_chunks:
+        raise ValueError(f"context needs {need} key chunks, the batch was built for {b.max_chunks}")
+    b.row_pos.copy_(torch.tensor(pos, dtype=torch.int32), non_blocking=True)
+    b.row_nkeys.copy_(torch.tensor(nk, dtype=torch.int32), non_blocking=True)
+
+
 def make_batch(st: State, widths: Sequence[int], device, max_chunks: int | None = None) -> Batch:
     widths = [int(x) for x in widths]
     if len(widths) != st.n_seqs or any(x < 0 for x in widths) or sum(widths) < 1:
@@ -182,11 +203,7 @@ def make_batch(st: State, widths: Sequence[int], device, max_chunks: int | None 
     rows = sum(widths)
     if rows > MAX_ROWS:
         raise ValueError(f"a forward takes at most {MAX_ROWS} packed rows, got {rows}")
-    starts, seq, idx, pos, nk = [0], [], [], [], []
-    for s, wd in enumerate(widths):
-        starts.append(starts[-1] + wd)
-        for t in range(wd):
-            seq.append(s); idx.append(t); pos.append(st.lens[s] + t); nk.append(st.lens[s] + t + 1)
+    starts, seq, idx, pos, nk = _batch_lists(st, widths)
     need = max(-(-(st.lens[s] + wd) // LA.CHUNK) for s, wd in enumerate(widths))
     def i32(v):
         return torch.tensor(v, dtype=torch.int32).to(device, non_blocking=True)
@@ -210,12 +227,15 @@ class Record:
 
 @torch.no_grad()
 def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_logits: bool = True,
-                 max_chunks: int | None = None, batch: Batch | None = None):
+                 max_chunks: int | None = None, batch: Batch | None = None, tp=None):
     """Logits (rows, vocab) bf16 for the window rows, and the record ``commit`` needs.
 
     ``windows``: one window width per sequence of ``st`` (packed rows are each sequence's chain in
     order), or, for a single sequence, the reference's ``parents`` list of a chain ([-1, 0, 1, ...]).
     The state is untouched. ``full_logits=False`` returns the final-normed hidden rows instead.
+    ``tp``: a ``distributed.RankGroup`` when ``w`` is one rank's shard: the output and down projections
+    then return fp32 partials, every rank gathers all of them and the next norm adds them in rank order
+    (two collectives a layer); the logits are this rank's slice of the vocabulary.
     """
 
     c = w.config
@@ -251,11 +271,17 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
     scale = c.head_dim ** -0.5
 
+    def row_parallel(act, weight):
+        """(residual rows, gathered partials): one of the two is None."""
+        if tp is None:
+            return lane_matmul(act, weight), None
+        return None, tp.gather_partials(lane_matmul(act, weight, f32=True))
+
     x = lane_glue.embed(tokens.to(torch.int32), *w.embed, c.hidden, g)
-    pending = None
+    pending = parts = None
     gi = ai = 0
     for layer in w.layers:
-        x, h = lane_glue.norm_xs(x, pending, layer.input_norm, c.eps, group=g)
+        x, h = lane_glue.norm_xs(x, pending, layer.input_norm, c.eps, group=g, partials=parts)
         if layer.linear:
             proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi])
             qkv, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
@@ -278,15 +304,15 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
                               scratch=scratch, out=o_att)
             mixed = lane_glue.gate_mul(o_att, proj[:, :nq], heads=c.heads, head_dim=c.head_dim, group=g)
             ai += 1
-        r = lane_matmul(mixed, layer.out_proj)
-        x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g)
+        r, rparts = row_parallel(mixed, layer.out_proj)
+        x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts)
         gu = lane_matmul(h, layer.gate_up, out=mlp_in)
         act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)
-        pending = lane_matmul(act, layer.down)
+        pending, parts = row_parallel(act, layer.down)
     if not full_logits:
-        _, hrows = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, rows_out=True, packed_out=False)
+        _, hrows = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, rows_out=True, packed_out=False, partials=parts)
         return hrows, rec
-    _, h = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g)
+    _, h = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, partials=parts)
     return lane_matmul(h, w.head), rec
 
 
@@ -324,4 +350,4 @@ def accept_path(drafted: Sequence[int], verified: Sequence[int]) -> int:
 
 
 __all__ = ["Batch", "Config", "LayerWeights", "Record", "State", "Weights", "accept_path", "commit", "load_weights",
-           "make_batch", "tree_forward"]
+           "make_batch", "refresh_batch", "tree_forward"]

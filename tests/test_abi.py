@@ -20,7 +20,7 @@ def test_header_and_loader_agree(lib):
     assert names, "no declarations found in the header"
     assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
     for name in names:
-        assert isinstance(getattr(lib, name), ctypes._CFuncPtr)
+        assert isinstance(getattr(lib.cdll, name), ctypes._CFuncPtr)
 
 
 def test_pure_host_entry_points(lib):

@@ -1,0 +1,103 @@
+"""Tensor-parallel host logic without a GPU: the partition map, the rank-ordered partial sum over a
+real two-process gloo group, and the vocabulary-split candidate merge.
+
+After the reference's ``tests/cuda/test_qwen27_distributed.py:36-91,140-190`` (partition map on CPU, gloo pair
+via ``torch.multiprocessing.spawn``) and ``test_qwen27_split_sampling.py`` (split == whole-vocabulary draw).
+"""
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import lane_oracle as O
+from tensorfold_b200 import distributed as D
+from tensorfold_b200 import distributed_head as H
+from tensorfold_b200 import exact_sampling as S
+from tensorfold_b200.forward import Config
+
+C27 = dict(hidden=5120, intermediate=17408, layers=64, heads=24, kv_heads=4, head_dim=256, vocab=248320, k_heads=16, v_heads=32)
+
+
+def test_shard_config_splits_heads_and_replicates_kv():
+    cfg = Config(**C27)
+    assert D.shard_config(cfg, 0, 1) is cfg
+    s2, s4, s8 = (D.shard_config(cfg, 0, w) for w in (2, 4, 8))
+    assert (s2.heads, s2.kv_heads, s2.k_heads, s2.v_heads, s2.intermediate, s2.vocab) == (12, 2, 8, 16, 8704, 124160)
+    assert (s4.heads, s4.kv_heads) == (6, 1)
+    assert (s8.heads, s8.kv_heads, s8.intermediate, s8.vocab) == (3, 1, 2176, 31040)     # 4 KV heads on 8 ranks: replicated
+    assert [list(D.kv_head_of_rank(cfg, r, 8)) for r in range(8)] == [[0], [0], [1], [1], [2], [2], [3], [3]]
+    assert [list(D.kv_head_of_rank(cfg, r, 2)) for r in range(2)] == [[0, 1], [2, 3]]
+    # every rank's query heads belong to the KV head it holds
+    for r in range(8):
+        q_heads = range(r * 3, r * 3 + 3)
+        assert {h // 6 for h in q_heads} == set(D.kv_head_of_rank(cfg, r, 8))
+    with pytest.raises(ValueError):
+        D.shard_config(cfg, 0, 5)
+    with pytest.raises(ValueError):
+        D.shard_config(cfg, 3, 2)
+
+
+def test_sum_rank_partials_rounds_once():
+    # the reference's example: three small addends survive only if the sum is rounded once, at the end
+    a, b = torch.full((2, 4), 1.0), torch.full((2, 4), 0.003)
+    parts = torch.stack([a, b, b])
+    assert torch.equal(D.sum_rank_partials(parts), (a + b + b).to(torch.bfloat16))
+    assert not torch.equal(D.sum_rank_partials(parts), ((a.bfloat16() + b.bfloat16()) + b.bfloat16()))
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        tp = D.RankGroup()
+        local = torch.full((3, 8), float(rank + 1))
+        local[0, 0] = 2.0 ** -9 if rank else 1.0
+        gathered = tp.gather_partials(local)
+        assert gathered.shape == (world, 3, 8)
+        total = D.sum_rank_partials(gathered)
+        # vocabulary-split greedy pick: rank r holds ids [r*5, r*5+5)
+        logits = torch.tensor([[0.0, 1.0, 3.0, 3.0, 2.0]]) if rank == 0 else torch.tensor([[3.0, 0.5, 0.0, 4.0, 4.0]])
+        val, idx = logits.max(dim=-1, keepdim=True)
+        all_idx = torch.empty((world, 1, 1), dtype=torch.int64)
+        all_val = torch.empty((world, 1, 1))
+        dist.all_gather_into_tensor(all_idx.view(-1, 1), (idx + rank * 5).contiguous())
+        dist.all_gather_into_tensor(all_val.view(-1, 1), val.contiguous())
+        midx, _ = H.merge_candidates(all_idx, all_val, 1)
+        out[rank] = (gathered[:, 0, 0].tolist(), total[0, 0].item(), int(midx[0, 0]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gloo_two_ranks_gather_in_rank_order():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    for rank in range(2):
+        first, total, pick = out[rank]
+        assert first == [1.0, 2.0 ** -9]                    # rank 0's partial first on every rank
+        assert total == float(torch.tensor(1.0 + 2.0 ** -9).bfloat16())
+        assert pick == 8                                    # 4.0 at global ids 8 and 9: the lower id wins
+
+
+def test_split_vocabulary_candidates_contain_the_whole_vocabulary_draw():
+    rng = np.random.default_rng(3)
+    vocab, world, rows = 4000, 4, 12
+    logits = np.round(rng.normal(size=(rows, vocab)) * 4) / 4
+    s = S.Sampling(seed=77, top_k=20, top_p=0.9)
+    positions = rng.integers(0, 10000, size=rows)
+    whole = O.sample_rows(logits.astype(np.float32), positions, O.Sampling(seed=77, top_k=20, top_p=0.9))
+    per = vocab // world
+    idx, val = [], []
+    for r in range(world):
+        i, v = O.topk_rows(logits[:, r * per:(r + 1) * per], 28)
+        idx.append(torch.from_numpy(i.astype(np.int64) + r * per)); val.append(torch.from_numpy(v))
+    midx, mval = H.merge_candidates(torch.stack(idx), torch.stack(val), 28)
+    wi, wv = O.topk_rows(logits, 28)
+    assert np.array_equal(midx.numpy(), wi) and np.array_equal(mval.numpy(), wv)
+    assert S.choose_rows(mval.numpy(), midx.numpy(), positions, s) == whole
