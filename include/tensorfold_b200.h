@@ -188,6 +188,24 @@ int tf_lane_attention_paged(const void* q, const void* k_new, const void* v_new,
                             int rows, int n_seqs, int max_window, int max_chunks, int heads, int kv_heads, int head_dim,
                             float scale, void* stream);
 
+/* The same attention for callers that cannot allocate or pass scratch: a server whose device memory
+ * was handed out once at start-up, a plugin inside a runtime that forbids allocation on the serving
+ * path, code for which every buffer address must be fixed in advance. This entry point has no
+ * counterpart in the TensorFold reference. The chunk partials live in a fixed array inside the
+ * loaded library (TF_ATTN_STATIC_SCRATCH_BYTES on every GPU that loads it, until the process exits);
+ * the call allocates nothing. Limits: tf_attention_scratch_bytes(rows, heads, head_dim, max_chunks)
+ * must not exceed TF_ATTN_STATIC_SCRATCH_BYTES, else TF_ESCRATCH and nothing runs. The first call on
+ * each device looks up the array's device address; make that call before any stream capture. All
+ * calls share the array: calls that overlap on one GPU race and must be serialised by the caller;
+ * stale contents from earlier calls are never read, so nothing needs clearing. Results are
+ * bit-identical to tf_lane_attention_paged. */
+#define TF_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+int tf_lane_attention_paged_static(const void* q, const void* k_new, const void* v_new, const void* k_pages,
+                                   const void* v_pages, const int* page_table, int max_pages, const int* seq_lens,
+                                   const int* seq_start, const int* row_nkeys, void* out, int rows, int n_seqs,
+                                   int max_window, int max_chunks, int heads, int kv_heads, int head_dim, float scale,
+                                   void* stream);
+
 /* Commit: copy the first keep[s] window rows of each sequence into its pages at positions
  * seq_lens[s].., for `layers` layers in one launch.
  * Replaces: families/qwen3_5/cuda/forward.py:237-251 (key/value rows in commit). */

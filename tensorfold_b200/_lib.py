@@ -54,6 +54,9 @@ SIGNATURES: dict[str, tuple] = {
     "tf_lane_attention_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_float, c_void_p]),
+    "tf_lane_attention_paged_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                               c_float, c_void_p]),
     "tf_kv_commit": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -103,7 +106,7 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
-            setattr(bound, name, fn if name in _NO_LAUNCH else _Counted(fn, 2 if name == "tf_lane_attention_paged" else 1))
+            setattr(bound, name, fn if name in _NO_LAUNCH else _Counted(fn, 2 if name.startswith("tf_lane_attention_paged") else 1))
         bound.cdll = lib
         _lib = bound
     return _lib

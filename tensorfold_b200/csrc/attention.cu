@@ -14,6 +14,8 @@
 // (page, head) is a contiguous 16 x D block. Masked-out keys never contribute: their scores are
 // -inf and their V rows are loaded as zeros.
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace tf {
@@ -351,3 +353,73 @@ int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, voi
 }
 
 }  // extern "C"
+
+// ---- the same attention for callers that may not allocate ------------------------------------------
+// Some hosts of this library cannot hand it a scratch buffer: an inference server whose device memory
+// is carved up once at start-up by its own pool and never grown, a plugin loaded into a runtime that
+// forbids cudaMalloc on the serving path (an allocation synchronises the whole device and can fail when
+// the pool already owns the memory), or code running inside a region where every buffer address must be
+// known in advance. For them the chunk partials live in the fixed array below, which is part of the
+// loaded module: every GPU that loads the library holds these bytes until the process exits.
+//
+// Rules that follow from one shared array: a call needs at most TF_ATTN_STATIC_SCRATCH_BYTES of
+// partials (more is refused, nothing runs); the array keeps whatever the previous call left, which is
+// harmless here because the merge kernel reads only entries the chunk kernel wrote in the same call, so
+// nothing has to be cleared; and two calls that overlap on one GPU (different streams, or threads)
+// would overwrite each other's partials — callers must serialise them.
+static __device__ __align__(256) unsigned char g_static_partials[TF_ATTN_STATIC_SCRATCH_BYTES];
+
+namespace tf {
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_lock;
+void* g_static_addr[kMaxDevices];        // device address of g_static_partials, per device; null = not looked up yet
+
+// The array's name is only a host-side handle here; kernels need its address on the device that is
+// current, which the runtime resolves once per device.
+int static_partials(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return TF_ECUDA; }
+    std::lock_guard<std::mutex> hold(g_static_lock);
+    if (g_static_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_partials) != cudaSuccess || p == nullptr) { cudaGetLastError(); return TF_ECUDA; }
+        g_static_addr[dev] = p;
+    }
+    *out = g_static_addr[dev];
+    return TF_OK;
+}
+}  // namespace
+}  // namespace tf
+
+extern "C" int tf_lane_attention_paged_static(const void* q, const void* k_new, const void* v_new, const void* k_pages,
+                                              const void* v_pages, const int* page_table, int max_pages, const int* seq_lens,
+                                              const int* seq_start, const int* row_nkeys, void* out, int rows, int n_seqs,
+                                              int max_window, int max_chunks, int heads, int kv_heads, int head_dim, float scale,
+                                              void* stream) {
+    if (rows < 1 || n_seqs < 1 || max_window < 1 || max_chunks < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads) return TF_EINVAL;
+    if ((head_dim != 128 && head_dim != 256) || heads / kv_heads > 16 || !(scale > 0.f)) return TF_EINVAL;
+    if (!q || !k_new || !v_new || !k_pages || !v_pages || !page_table || !seq_lens || !seq_start || !row_nkeys || !out) return TF_EINVAL;
+    if (((uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return TF_EALIGN;
+    // too many rows x heads x chunks for the fixed array: refuse before anything is queued
+    if (tf_attention_scratch_bytes(rows, heads, head_dim, max_chunks) > (size_t)TF_ATTN_STATIC_SCRATCH_BYTES) return TF_ESCRATCH;
+    void* scratch = nullptr;
+    const int rc = tf::static_partials(&scratch);
+    if (rc != TF_OK) return rc;
+    const int G = heads / kv_heads;
+    tf::AttnArgs a;
+    a.q = static_cast<const __nv_bfloat16*>(q);
+    a.k_new = static_cast<const __nv_bfloat16*>(k_new); a.v_new = static_cast<const __nv_bfloat16*>(v_new);
+    a.k_pages = static_cast<const __nv_bfloat16*>(k_pages); a.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    a.page_table = page_table; a.seq_lens = seq_lens; a.seq_start = seq_start;
+    float* sc = static_cast<float*>(scratch);
+    const size_t nrh = (size_t)max_chunks * rows * heads;
+    a.part_o = sc; a.part_m = sc + nrh * head_dim; a.part_l = a.part_m + nrh;
+    a.max_pages = max_pages; a.H = heads; a.HK = kv_heads; a.R = rows;
+    a.qgroups = (max_window * G + tf::kQRows - 1) / tf::kQRows;
+    a.scale_log2 = scale * tf::kLog2e;
+    if ((long long)n_seqs * a.qgroups > 65535) return TF_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return head_dim == 256 ? tf::run<256>(a, n_seqs, max_chunks, row_nkeys, out, st)
+                           : tf::run<128>(a, n_seqs, max_chunks, row_nkeys, out, st);
+}
