@@ -84,6 +84,32 @@ int tf_qmm_untile(const void* w_tiled, void* words, void* scales, void* biases, 
                   void* stream);
 
 
+/* ---- prefill-width 4-bit matmul on tcgen05 tensor cores ---------------------------------------
+ * Replaces: the dense bf16 GEMM the reference's prompt prefill runs after dequantising a layer
+ * (families/qwen3_5/cuda/forward.py prefill path; runtime/serve.py prompt admission) — a PHASE of a
+ * request, chosen by the caller, never by the row count of a verify window.
+ *
+ * Same formula as tf_qmm, different arithmetic, hence different bits: each activation is carried as
+ * two e4m3 planes hi + lo of x * 2^E (E a power of two per row and group that brings the group's
+ * largest magnitude into [128, 256)), the 4-bit weight codes are the e4m3 values q * 2^-9, and the
+ * products are summed by tcgen05.mma kind::f8f6f4 into fp32 accumulators in tensor memory. Results
+ * are within the bf16 bound of tf_qmm's (|x| below 2^-8 of its group's largest lose precision) and
+ * are independent of the number of rows in the call within this kernel; a request's serial decode
+ * and verify windows must not mix it with tf_qmm.
+ *
+ * x_packed: tf_packed_tc_bytes bytes from tf_pack_rows_tc; w_tiled: tf_qmm_tc_tiled_bytes bytes from
+ * tf_qmm_tc_tile (a different order from tf_qmm_tile's). scratch as for tf_qmm. M is 1..128. */
+size_t tf_packed_tc_bytes(int M, int K, int group);
+size_t tf_qmm_tc_tiled_bytes(int N, int K, int group);
+int tf_qmm_tc(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
+              int K, int group, int flags, int* status, void* stream);
+int tf_pack_rows_tc(const void* x, void* x_packed, void* xs, int M, int K, int group, void* stream);
+int tf_qmm_tc_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,
+                   void* stream);
+int tf_qmm_tc_untile(const void* w_tiled, void* words, void* scales, void* biases, int N, int K, int group,
+                     void* stream);
+
+
 /* ---- glue: the steps between two matmuls ----------------------------------------------------
  * Each writes the next matmul's input in packed form (group sums included) when given a packed
  * output, and/or plain row-major bf16. M is 1..128 rows. Strides are in elements. */

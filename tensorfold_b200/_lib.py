@@ -32,6 +32,13 @@ SIGNATURES: dict[str, tuple] = {
     "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_packed_tc_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_qmm_tc_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_qmm_tc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
+                          c_void_p, c_void_p]),
+    "tf_pack_rows_tc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_qmm_tc_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_qmm_tc_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_norm_xs": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_int, c_float, c_void_p]),
     "tf_swiglu": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -67,7 +74,7 @@ SIGNATURES: dict[str, tuple] = {
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
 _NO_LAUNCH = {"tf_version", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes"}
+              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes"}
 
 
 def launch_count() -> int:
