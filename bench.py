@@ -139,17 +139,58 @@ def cpu_reference(args, rows: int):
                       f"{rows} rows, scaled to 48 + 16 layers + head by weight count"}
 
 
+def only_qmm(args, dev):
+    """The lane matmul alone: --copies weights of --shape rotated through so that every launch streams
+    from HBM; CUDA-event time per launch, algorithmic bytes, fraction of the measured copy bandwidth."""
+
+    import torch
+
+    from tensorfold_b200 import _lib, lane_qmm, synthetic
+
+    n, k = (int(v) for v in args.shape.split("x"))
+    group, rows = 64, args.rows
+    gen = torch.Generator(device=dev).manual_seed(3)
+    ws = [synthetic.random_q4(gen, n, k, group, dev) for _ in range(args.copies)]
+    x = lane_qmm.pack_rows(torch.randn((rows, k), device=dev, generator=gen).to(torch.bfloat16), group)
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    for q in ws:
+        lane_qmm.lane_matmul(x, q, out=out)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = max(args.steps, 1) * args.copies
+    e0.record()
+    for i in range(launches):
+        lane_qmm.lane_matmul(x, ws[i % args.copies], out=out)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    _lib.status(dev).raise_if_set()
+    us = 1000.0 * e0.elapsed_time(e1) / launches
+    kg = k // group
+    alg = n * k // 2 + n * kg * 4 + rows * k * 2 + rows * kg * 4 + rows * n * 2
+    peak, kind = peaks()
+    print(json.dumps({"only": "qmm", "shape": [n, k], "rows": rows, "launches": launches, "us_per_launch": us,
+                      "note": "eager launches back to back (includes launch gaps); the graph-replayed figure is in the main line",
+                      "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--seqs", type=int, default=16)
+    ap.add_argument("--seqs", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--width", type=int, default=8)
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--synthetic-context", action="store_true",
+                    help="skip the prefill: set the context length directly (KV pages and recurrent state stay zero); for profiler runs")
+    ap.add_argument("--no-spinup", action="store_true", help="skip the half second of untimed steps that brings the clocks up")
+    ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit")
+    ap.add_argument("--shape", default="17408x5120")
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--copies", type=int, default=4, help="--only qmm: weight copies rotated through (4 x 50 MB > L2)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -191,6 +232,9 @@ def main():
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
 
+    if args.only == "qmm":
+        return only_qmm(args, dev)
+
     spec = dict(synthetic.DENSE_27B, layers=args.layers)
     cfg = F.Config(**spec)
     w = synthetic.random_weights(cfg, seed=2, device=dev, rank=rank, world=world)
@@ -201,6 +245,9 @@ def main():
     # ---- context: real prefill, W rows per sequence per replay, through the captured step ----
     gen = torch.Generator(device=dev).manual_seed(7)
     full = [args.width] * args.seqs
+    if args.synthetic_context:
+        st.lens = [args.ctx] * args.seqs
+        run.refresh()
     while st.lens[0] + args.width <= args.ctx:
         run.tokens.copy_(torch.randint(0, cfg.vocab, (rows,), generator=gen, device=dev, dtype=torch.int32))
         run.step_device()
@@ -221,7 +268,7 @@ def main():
     for _ in range(max(args.warmup, 3)):
         run.step_device()
     # spin the clocks up: short bursts right after idle run at low clocks
-    t_end = time.time() + 0.5
+    t_end = time.time() + (0.0 if args.no_spinup else 0.5)
     while time.time() < t_end:
         run.step_device()
         torch.cuda.synchronize(dev)

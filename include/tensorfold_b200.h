@@ -241,9 +241,12 @@ int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, voi
 
 /* ---- exact top-k and keyed sampling --------------------------------------------------------------
  * Each row's k largest bf16 logits (k <= 64), ordered by value descending then id ascending; ties at
- * the cut go to the smallest ids. idx int32 [rows, k], val fp32 [rows, k].
+ * the cut go to the smallest ids. idx int32 [rows, k], val fp32 [rows, k]. scratch: the slices'
+ * candidates, tf_topk_scratch_bytes bytes, 8-byte aligned, no initialisation; two launches.
  * Replaces: engine/topk.py:20-146 (radix_topk, topk_rows). */
-int tf_topk_rows(const void* x, size_t row_stride, int rows, int vocab, int k, int* idx, float* val, void* stream);
+size_t tf_topk_scratch_bytes(int rows, int vocab, int k);
+int tf_topk_rows(const void* x, size_t row_stride, int rows, int vocab, int k, int* idx, float* val, void* scratch,
+                 size_t scratch_bytes, void* stream);
 
 /* token = argmax over the kept candidates of val/temperature + Gumbel(splitmix64(seed, position, id));
  * candidates (already ordered as tf_topk_rows writes them) are cut to top_k, then to the smallest

@@ -66,7 +66,8 @@ SIGNATURES: dict[str, tuple] = {
                                                c_float, c_void_p]),
     "tf_kv_commit": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
-    "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "tf_topk_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tf_sample_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_ulonglong, c_double, c_int, c_double, c_void_p,
                                c_int, c_void_p]),
 }
@@ -74,7 +75,7 @@ SIGNATURES: dict[str, tuple] = {
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
 _NO_LAUNCH = {"tf_version", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes"}
+              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes"}
 
 
 def launch_count() -> int:
@@ -82,7 +83,7 @@ def launch_count() -> int:
 
 
 class _Counted:
-    """A bound entry point that counts successful kernel launches (tf_lane_attention_paged queues two)."""
+    """A bound entry point that counts successful kernel launches (the paged attention and the top-k queue two each)."""
 
     def __init__(self, fn, n):
         self.fn, self.n = fn, n
@@ -113,7 +114,7 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
-            setattr(bound, name, fn if name in _NO_LAUNCH else _Counted(fn, 2 if name.startswith("tf_lane_attention_paged") else 1))
+            setattr(bound, name, fn if name in _NO_LAUNCH else _Counted(fn, 2 if name.startswith("tf_lane_attention_paged") or name == "tf_topk_rows" else 1))
         bound.cdll = lib
         _lib = bound
     return _lib

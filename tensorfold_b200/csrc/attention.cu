@@ -264,20 +264,6 @@ __global__ void kv_commit_kernel(const __nv_bfloat16* k_new, const __nv_bfloat16
     }
 }
 
-inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelExC(&cfg, fn, args);
-}
-
 template <int D>
 int run(const AttnArgs& a, int n_seqs, int max_chunks, const int* row_nkeys, void* out, cudaStream_t st) {
     constexpr size_t smem = (size_t)(kQRows + 4 * kTileKeys) * D * 2;

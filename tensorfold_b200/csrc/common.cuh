@@ -8,6 +8,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <stdint.h>
 
 #include "../../include/tensorfold_b200.h"
@@ -152,5 +154,32 @@ __device__ __forceinline__ float warp_max(float v) {
 // let the next grid start its prologue once this one has passed its own wait.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- launches ------------------------------------------------------------------------------------
+// Kernels can be launched with programmatic stream serialisation: a kernel may then become resident
+// while its predecessor still runs, do its input-independent work (barrier setup, weight prefetch)
+// and block in pdl_wait() until the predecessor's memory is visible. Measured on B200 this helps a
+// chain of matmuls (about 2 us a launch) but slows a whole forward, where small kernels sit between
+// them, by 20-40%; so it is off unless TF_PDL is set: bit 0 for the small kernels, bit 1 for the matmuls.
+// Without the attribute pdl_wait() and pdl_launch_dependents() do nothing.
+inline int pdl_mode() {
+    static const int mode = [] { const char* e = std::getenv("TF_PDL"); return e ? (e[0] - '0') : 0; }();
+    return mode;
+}
+inline bool pdl_enabled(bool matmul = false) { return (pdl_mode() & (matmul ? 2 : 1)) != 0; }
+
+inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelExC(&cfg, fn, args);
+}
 
 }  // namespace tf

@@ -157,19 +157,6 @@ __global__ void conv_commit_kernel(const __nv_bfloat16* qkv, size_t qkv_stride, 
     for (int i = 0; i < 3; ++i) *reinterpret_cast<uint4*>(st + (size_t)i * C) = out[i];
 }
 
-inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, cudaStream_t st, void** args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelExC(&cfg, fn, args);
-}
-
 int check(int S, int layers, int KH, int VH, int DK, int DV) {
     if (S < 1 || layers < 1 || KH < 1 || VH < 1 || VH % KH || DK != kDk || DV < 1 || DV % kRowsPerCta) return TF_EINVAL;
     if ((long long)S * layers > 65535) return TF_EINVAL;
@@ -195,7 +182,7 @@ int tf_gdn_chain(const void* q, const void* k, const void* v, const float* g, co
     a.KH = k_heads; a.VH = v_heads; a.DV = dv; a.S = n_seqs;
     void* args[] = {&a};
     dim3 grid((dv + tf::kRowsPerCta - 1) / tf::kRowsPerCta, v_heads, n_seqs);
-    cudaError_t e = tf::launch_pdl((const void*)tf::gdn_kernel<true>, grid, dim3(tf::kRowsPerCta * 4),
+    cudaError_t e = tf::launch_pdl((const void*)tf::gdn_kernel<true>, grid, dim3(tf::kRowsPerCta * 4), 0,
                                    static_cast<cudaStream_t>(stream), args);
     if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
@@ -216,7 +203,7 @@ int tf_gdn_replay(const void* k, const void* v, const float* g, const float* bet
     a.rec_q = rec_k_stride; a.rec_v = rec_v_stride; a.rec_g = rec_g_stride; a.rec_state = state_stride;
     void* args[] = {&a};
     dim3 grid((dv + tf::kRowsPerCta - 1) / tf::kRowsPerCta, v_heads, n_seqs * layers);
-    cudaError_t e = tf::launch_pdl((const void*)tf::gdn_kernel<false>, grid, dim3(tf::kRowsPerCta * 4),
+    cudaError_t e = tf::launch_pdl((const void*)tf::gdn_kernel<false>, grid, dim3(tf::kRowsPerCta * 4), 0,
                                    static_cast<cudaStream_t>(stream), args);
     if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
@@ -229,7 +216,7 @@ int tf_conv_commit(const void* qkv, size_t qkv_stride, long long rec_qkv_stride,
     if (((uintptr_t)qkv | (uintptr_t)conv_state) & 15 || rec_qkv_stride % 8 || state_stride % 8) return TF_EALIGN;
     void* args[] = {&qkv, &qkv_stride, &rec_qkv_stride, &conv_state, &state_stride, &seq_start, &keep, &channels, &n_seqs};
     dim3 grid((channels / 8 + 127) / 128, 1, n_seqs * layers);
-    cudaError_t e = tf::launch_pdl((const void*)tf::conv_commit_kernel, grid, dim3(128), static_cast<cudaStream_t>(stream), args);
+    cudaError_t e = tf::launch_pdl((const void*)tf::conv_commit_kernel, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), args);
     if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
 }

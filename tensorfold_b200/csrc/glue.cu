@@ -294,20 +294,6 @@ __global__ void embed_kernel(const int* ids, const uint32_t* words, const __nv_b
     reinterpret_cast<uint4*>(out)[(size_t)row * (D >> 3) + c] = pack8(v);
 }
 
-inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelExC(&cfg, fn, args);
-}
-
 inline int finish(cudaError_t e) {
     if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;

@@ -11,8 +11,8 @@
 //   then one rounding to bf16.
 // The chain never looks at the row count, so row m of an M-row call has the bits of a 1-row call.
 //
-// Weight tile layout (built by tf_qmm_tile): records indexed [column block of 128][k tile of 64]
-// [column tile of 16 inside the block]; a pipeline stage (all 8 column tiles of a block, a few k
+// Weight tile layout (built by tf_qmm_tile): records indexed [column block of 256][k tile of 64]
+// [column tile of 16 inside the block]; a pipeline stage (all 16 column tiles of a block, a few k
 // tiles) is therefore ONE contiguous range and arrives with a single bulk copy. Each record is
 // 512 bytes of nibbles + 64*(64/group) bytes of (scale, bias) pairs.
 //   nibbles: lane (g = lane/4, t = lane%4) owns 16 bytes = 4 words; word s (k-step s) holds, at
@@ -28,7 +28,7 @@
 // over all banks), then the tile's group sums as [groups in tile][Mp] fp32. A stage's activations
 // are again one contiguous range.
 //
-// Warp roles in a CTA: 8 consumer warps (one 16-column tile each), one producer thread (bulk
+// Warp roles in a CTA: 16 consumer warps (one 16-column tile each), one producer thread (bulk
 // copies), one finisher warp that sums parked K segments so the consumers never wait on a fence.
 
 #include "common.cuh"
@@ -39,7 +39,7 @@ namespace {
 constexpr int kWorkers = 148;
 constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every row bucket, so that the
                                 // K segments (hence the bits) do not depend on the row count
-constexpr int kWarps = 8;       // consumer warps = column tiles per column block (baked into the layout)
+constexpr int kWarps = 16;      // consumer warps = column tiles per column block (baked into the layout)
 constexpr int kCols = kWarps * 16;
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 512 + (64 / group) * 64; }
@@ -80,13 +80,24 @@ __host__ __device__ inline int owner_of(int w, int total) { return (int)((((long
 constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
 
 // A parked K segment of column block `cb` is complete in global memory: take a ticket; the last of
-// the block's segments to arrive adds them all in k order and writes the output. One warp.
-__device__ void finish_segment(const Args& a, int cb, int SPB, int total, int lane, int* list) {
+// the block's segments to arrive adds them all in k order and writes the output. Run by NT threads:
+// the finisher warp (NT = 32) for a segment at the start of a CTA's range, while the consumers go on,
+// or all consumer warps together for the segment that ends the range, when they have nothing left
+// to do and the sum is on the kernel's critical path.
+template <int NT>
+__device__ __forceinline__ void group_sync() {
+    if (NT == 32) __syncwarp();
+    else named_bar_sync(1, NT);
+}
+
+template <int NT>
+__device__ void finish_segment(const Args& a, int cb, int SPB, int total, int tid, int* list) {
     __threadfence();
+    group_sync<NT>();
     const int cb_begin = cb * SPB;
-    const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
-    int nseg = 0;
-    if (lane == 0) {
+    if (tid == 0) {
+        const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
+        int nseg = 0;
         for (int o = first; o <= last; ++o) {
             const int ob = range_begin(o, total);
             if (ob == range_begin(o + 1, total)) continue;       // a worker without work
@@ -95,14 +106,14 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int la
         list[kWorkers] = nseg;
         list[kWorkers + 1] = atomicAdd(a.counters + cb, 1);
     }
-    __syncwarp();
-    nseg = list[kWorkers];
+    group_sync<NT>();
+    const int nseg = list[kWorkers];
     if (list[kWorkers + 1] != nseg - 1) return;
     __threadfence();
     const int ncol4 = (min(kCols, a.N - cb * kCols) + 3) >> 2;
     const int n4 = a.M * (kCols / 4);
-    constexpr int U = 4;          // elements in flight per lane
-    for (int base = lane; base < n4; base += 32 * U) {
+    constexpr int U = 4;          // elements in flight per thread and segment
+    for (int base = tid; base < n4; base += NT * U) {
         float4 sum[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -112,7 +123,7 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int la
             for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int idx = base + 32 * u;
+                    const int idx = base + NT * u;
                     v[jj][u] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (j + jj < nseg && idx < n4)
                         v[jj][u] = __ldcg(reinterpret_cast<const float4*>(a.slots + (size_t)list[j + jj] * kSlotFloats) + idx);
@@ -129,7 +140,7 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int la
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int idx = base + 32 * u;
+            const int idx = base + NT * u;
             if (idx >= n4) continue;
             const int row = idx / (kCols / 4), c4 = idx - row * (kCols / 4);
             if (c4 >= ncol4) continue;
@@ -144,16 +155,15 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int la
             }
         }
     }
-    __syncwarp();
-    if (lane == 0) a.counters[cb] = 0;     // leave the counters zero for the next call
+    if (tid == 0) a.counters[cb] = 0;      // leave the counters zero for the next call (every reader is past its ticket)
 }
 
 template <int G, int MB, int KTS, int STAGES>
-__global__ void __launch_bounds__((kWarps + 2) * 32, (MB <= 2 ? 2 : 1)) qmm_kernel(const Args a) {
+__global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a) {
     using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ int seg_list[kWorkers + 2];
+    __shared__ int seg_list[2][kWorkers + 2];   // [0] finisher warp, [1] consumers
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K >> 6;                              // k tiles
     const int CB = (a.N + kCols - 1) / kCols;             // column blocks
@@ -178,8 +188,9 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, (MB <= 2 ? 2 : 1)) qmm_kern
 
     // the first and the last segment of this CTA's range may be parts of a column block
     const int cb_first = begin < end ? begin / SPB : 0, cb_last = begin < end ? (end - 1) / SPB : 0;
-    const bool part_first = begin > cb_first * SPB || end < (cb_first + 1) * SPB;
-    const bool part_last = cb_last != cb_first && end < (cb_last + 1) * SPB;
+    // a partial segment that ends the range is summed by the consumers themselves; one that starts a
+    // longer range goes to the finisher warp
+    const bool part_first = cb_last != cb_first && begin > cb_first * SPB;
 
     if (warp == kWarps) {
         // ------------------------------- producer: one thread ----------------------------------
@@ -229,11 +240,7 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, (MB <= 2 ? 2 : 1)) qmm_kern
         // ------------------- finisher: sums parked segments while the consumers go on -----------
         if (part_first) {
             named_bar_sync(2, (kWarps + 1) * 32);
-            finish_segment(a, cb_first, SPB, total, lane, seg_list);
-        }
-        if (part_last) {
-            named_bar_sync(3, (kWarps + 1) * 32);
-            finish_segment(a, cb_last, SPB, total, lane, seg_list);
+            finish_segment<32>(a, cb_first, SPB, total, lane, seg_list[0]);
         }
         return;
     }
@@ -331,9 +338,8 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, (MB <= 2 ? 2 : 1)) qmm_kern
                     const int row = rb * 8 + 2 * t + (i & 1);
                     if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
                 }
-            // hand over to the finisher warp without waiting for it
-            if (cb == cb_first) asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");
-            else asm volatile("bar.arrive 3, %0;" ::"r"((kWarps + 1) * 32) : "memory");
+            if (seg_end == end) finish_segment<kWarps * 32>(a, cb, SPB, total, threadIdx.x, seg_list[1]);
+            else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");   // the finisher takes it; go on
         }
     }
 }
@@ -358,18 +364,26 @@ int launch(const Args& a, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled(true) ? 1 : 0;
     if (cudaLaunchKernelEx(&cfg, kern, a) != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
 }
 
+template <int G, int MB, int KTS>
+constexpr int stages_for() {
+    constexpr int budget = 224 * 1024;
+    constexpr int stage = ((kWarps * KTS * rec_bytes(G) + KTS * MB * 8 * (128 + 4 * (64 / G)) + 127) / 128) * 128 + 16;
+    return budget / stage > 8 ? 8 : budget / stage;
+}
+
 template <int G>
 int dispatch(const Args& a, cudaStream_t stream) {
-    if (a.M <= 8) return launch<G, 1, 4, 4>(a, stream);      // two CTAs fit an SM: the next kernel's
-    if (a.M <= 16) return launch<G, 2, 4, 4>(a, stream);     // weight prefetch overlaps this one's tail
-    if (a.M <= 32) return launch<G, 4, 4, 6>(a, stream);
-    if (a.M <= 64) return launch<G, 8, 2, 6>(a, stream);
-    return launch<G, 16, 2, 5>(a, stream);
+    // one CTA per SM; the stage ring takes nearly all of shared memory (about 30 MB in flight chip-wide)
+    if (a.M <= 8) return launch<G, 1, 4, stages_for<G, 1, 4>()>(a, stream);
+    if (a.M <= 16) return launch<G, 2, 4, stages_for<G, 2, 4>()>(a, stream);
+    if (a.M <= 32) return launch<G, 4, 4, stages_for<G, 4, 4>()>(a, stream);
+    if (a.M <= 64) return launch<G, 8, 2, stages_for<G, 8, 2>()>(a, stream);
+    return launch<G, 16, 2, stages_for<G, 16, 2>()>(a, stream);
 }
 
 // ---- relayout kernels: one thread per output word / pair -----------------------------------------
@@ -473,7 +487,7 @@ size_t tf_packed_bytes(int M, int K, int group) {
 }
 
 size_t tf_qmm_scratch_bytes(void) {
-    // counters + two parked partial blocks (128 rows x 128 columns fp32) per worker
+    // counters + two parked partial blocks (128 rows x 256 columns fp32) per worker
     return TF_QMM_COUNTER_BYTES + (size_t)2 * tf::kWorkers * TF_QMM_MAX_ROWS * tf::kCols * sizeof(float);
 }
 

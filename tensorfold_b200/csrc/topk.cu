@@ -1,10 +1,12 @@
 // Exact top-k over vocabulary rows and the keyed Gumbel-max draw.
 //
-// top-k: a bf16 logit is a 16-bit sortable key. Two 256-bin histogram passes find the k-th largest
-// key T; a third pass collects everything above T plus the ties at T with the SMALLEST token ids;
-// the k survivors are ordered by (value descending, id ascending). Each thread scans a contiguous
-// slice of the row and a block-wide prefix sum places its finds, so the result is a function of the
-// row alone: no atomics decide which tie survives. One CTA per row.
+// top-k: a bf16 logit is a 16-bit sortable key. A row is cut into contiguous slices of at most 16384
+// entries, one CTA per (slice, row). The CTA stages its slice's keys in shared memory, finds the k-th
+// largest key T with two 256-bin histograms (high byte, then low byte), and keeps everything above T
+// plus the ties at T with the SMALLEST token ids: each thread scans a contiguous piece and a
+// block-wide prefix sum places its finds, so no atomic decides which tie survives. A second kernel
+// ranks the slices' candidates by (value descending, id ascending) and writes the first k. The row's
+// k largest are among its slices' k largest, so the result is exact and a function of the row alone.
 //
 // draw: token = argmax over the kept candidates of logit/T + Gumbel(hash(seed, position, id)), the
 // candidates being the top_k cut to the smallest prefix whose tempered probability reaches top_p.
@@ -16,12 +18,22 @@
 namespace tf {
 namespace {
 
-constexpr int kThreads = 1024, kMaxK = 64;
+constexpr int kMaxK = 64;
+constexpr int kSliceThreads = 256, kSliceMax = 16384, kMaxSlices = 64, kMergeThreads = 1024;
+
+__host__ __device__ inline int slice_len(int V) {
+    const int slices = (V + kSliceMax - 1) / kSliceMax;
+    return (((V + slices - 1) / slices) + 7) & ~7;          // a multiple of 8 entries: slices start 16-byte aligned
+}
+__host__ __device__ inline int slice_count(int V) { return (V + slice_len(V) - 1) / slice_len(V); }
 
 __device__ __forceinline__ uint32_t sort_key(uint32_t b) { return (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u); }
+__device__ __forceinline__ uint32_t unsort_key(uint32_t k) { return (k & 0x8000u) ? (k & 0x7FFFu) : (~k & 0xFFFFu); }
 
-// exclusive prefix sum of one int per thread over the CTA (1024 threads), fixed order
+// exclusive prefix sum of one int per thread over a CTA of NT threads, fixed order
+template <int NT>
 __device__ int block_scan(int v, int* warp_tot, int& total) {
+    constexpr int NW = NT / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int inc = v;
 #pragma unroll
@@ -32,13 +44,13 @@ __device__ int block_scan(int v, int* warp_tot, int& total) {
     if (lane == 31) warp_tot[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-        int w = warp_tot[lane], winc = w;
+        int w = lane < NW ? warp_tot[lane] : 0, winc = w;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int n = __shfl_up_sync(0xffffffffu, winc, o);
             if (lane >= o) winc += n;
         }
-        warp_tot[lane] = winc - w;
+        if (lane < NW) warp_tot[lane] = winc - w;
         if (lane == 31) warp_tot[32] = winc;
     }
     __syncthreads();
@@ -48,88 +60,111 @@ __device__ int block_scan(int v, int* warp_tot, int& total) {
     return base + inc - v;
 }
 
-__global__ void __launch_bounds__(kThreads) topk_kernel(const __nv_bfloat16* x, size_t row_stride, int V, int K, int* idx_out,
-                                                        float* val_out) {
+// One histogram pass over the staged keys: bin = byte `shift` of the keys that pass `keep`; lanes of a
+// warp that hit the same bin add once (logits crowd into a few exponents). Then the bin holding the
+// K-th largest is found: found[0] = bin, found[1] = entries in higher bins.
+template <class Keep>
+__device__ void select_byte(const uint16_t* keys, int n, int shift, int K, int above0, unsigned* hist, int* warp_tot, int* found,
+                            Keep keep) {
+    const int tid = threadIdx.x;
+    hist[tid] = 0;
+    __syncthreads();
+    const int padded = (n + kSliceThreads - 1) / kSliceThreads * kSliceThreads;
+    for (int i = tid; i < padded; i += kSliceThreads) {
+        const uint32_t key = i < n ? keys[i] : 0u;
+        const int bin = (i < n && keep(key)) ? (int)((key >> shift) & 0xFFu) : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (bin >= 0 && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+    }
+    __syncthreads();
+    // entries in bins above mine: an exclusive prefix sum over the bins in descending order
+    const int mine = (int)hist[255 - tid];
+    int total;
+    const int above = above0 + block_scan<kSliceThreads>(mine, warp_tot, total);
+    if (above < K && above + mine >= K) { found[0] = 255 - tid; found[1] = above; }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSliceThreads) topk_slice_kernel(const __nv_bfloat16* x, size_t row_stride, int V, int K, uint2* cand) {
+    __shared__ __align__(16) uint16_t keys[kSliceMax];
     __shared__ unsigned hist[256];
-    __shared__ int found[4];
+    __shared__ int found[2];
     __shared__ int warp_tot[33];
-    __shared__ uint32_t sel_key[kMaxK];
-    __shared__ int sel_idx[kMaxK];
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
-    const uint16_t* xr = reinterpret_cast<const uint16_t*>(x) + (size_t)row * row_stride;
-    const int per = (V + kThreads - 1) / kThreads;
-    const int lo = min(V, tid * per), hi = min(V, lo + per);       // this thread's contiguous slice
+    const int tid = threadIdx.x, row = blockIdx.y, L = slice_len(V);
+    const int v0 = blockIdx.x * L, n = min(L, V - v0);
+    const uint16_t* xr = reinterpret_cast<const uint16_t*>(x) + (size_t)row * row_stride + v0;
+    uint2* out = cand + ((size_t)row * gridDim.x + blockIdx.x) * K;
+    const int kk = min(K, n);                                   // a short slice yields all it has
+    for (int j = tid + kk; j < K; j += kSliceThreads) out[j] = make_uint2(0u, 0x7FFFFFFFu);   // ranks behind every real entry
 
-    // pass 1: histogram of the key's high byte (counts do not depend on the order they are added in)
-    for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < V; i += kThreads) atomicAdd(&hist[sort_key(xr[i]) >> 8], 1u);
-    __syncthreads();
-    if (tid == 0) {
-        unsigned above = 0;
-        int b = 255;
-        for (; b >= 0; --b) {
-            if (above + hist[b] >= (unsigned)K) break;
-            above += hist[b];
+    if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+        for (int i = tid * 8; i < n; i += kSliceThreads * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (i + 2 * j < n) keys[i + 2 * j] = (uint16_t)sort_key(w[j] & 0xFFFFu);
+                if (i + 2 * j + 1 < n) keys[i + 2 * j + 1] = (uint16_t)sort_key(w[j] >> 16);
+            }
         }
-        found[0] = max(b, 0);
-        found[2] = (int)above;
+    } else {
+        for (int i = tid; i < n; i += kSliceThreads) keys[i] = (uint16_t)sort_key(xr[i]);
     }
     __syncthreads();
+
+    select_byte(keys, n, 8, kk, 0, hist, warp_tot, found, [](uint32_t) { return true; });
     const uint32_t hb = (uint32_t)found[0];
+    const int above_hb = found[1];
     __syncthreads();
-    // pass 2: histogram of the low byte inside that high byte
-    for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < V; i += kThreads) {
-        const uint32_t key = sort_key(xr[i]);
-        if ((key >> 8) == hb) atomicAdd(&hist[key & 0xFFu], 1u);
-    }
-    __syncthreads();
-    if (tid == 0) {
-        unsigned above = (unsigned)found[2];
-        int b = 255;
-        for (; b >= 0; --b) {
-            if (above + hist[b] >= (unsigned)K) break;
-            above += hist[b];
-        }
-        found[1] = (int)((hb << 8) | (uint32_t)max(b, 0));
-        found[2] = (int)above;                 // elements strictly above the threshold key
-    }
-    __syncthreads();
-    const uint32_t T = (uint32_t)found[1];
-    const int above = found[2], need = K - above;
-    // pass 3: everything above T (slot = rank in id order), then the first `need` ties in id order
+    select_byte(keys, n, 0, kk, above_hb, hist, warp_tot, found, [hb](uint32_t key) { return (key >> 8) == hb; });
+    const uint32_t T = (hb << 8) | (uint32_t)found[0];
+    const int above = found[1], need = kk - above;              // entries strictly above T; ties still wanted
+
+    // everything above T, then the first `need` ties, both in id order
+    const int per = (n + kSliceThreads - 1) / kSliceThreads;
+    const int lo = min(n, tid * per), hi = min(n, lo + per);
     int n_above = 0, n_tie = 0;
     for (int i = lo; i < hi; ++i) {
-        const uint32_t key = sort_key(xr[i]);
+        const uint32_t key = keys[i];
         n_above += key > T;
         n_tie += key == T;
     }
     int total;
-    int at_above = block_scan(n_above, warp_tot, total);
-    int at_tie = block_scan(n_tie, warp_tot, total);
+    int at_above = block_scan<kSliceThreads>(n_above, warp_tot, total);
+    int at_tie = block_scan<kSliceThreads>(n_tie, warp_tot, total);
     for (int i = lo; i < hi; ++i) {
-        const uint32_t key = sort_key(xr[i]);
+        const uint32_t key = keys[i];
         if (key > T) {
-            if (at_above < kMaxK) { sel_key[at_above] = key; sel_idx[at_above] = i; }
-            ++at_above;
+            out[at_above++] = make_uint2(key, (uint32_t)(v0 + i));
         } else if (key == T) {
-            if (at_tie < need) { sel_key[above + at_tie] = key; sel_idx[above + at_tie] = i; }
+            if (at_tie < need) out[above + at_tie] = make_uint2(key, (uint32_t)(v0 + i));
             ++at_tie;
         }
     }
+}
+
+// One CTA per row: rank the slices' candidates by (key descending, id ascending); ranks are distinct.
+__global__ void __launch_bounds__(kMergeThreads) topk_merge_kernel(const uint2* cand, int n, int K, int* idx_out, float* val_out) {
+    __shared__ uint2 c[kMaxSlices * kMaxK];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    for (int i = threadIdx.x; i < n; i += kMergeThreads) c[i] = cand[(size_t)row * n + i];
     __syncthreads();
-    // order the K survivors: key descending, id ascending (rank by counting)
-    if (tid < K) {
-        const uint32_t kk = sel_key[tid];
-        const int ii = sel_idx[tid];
+    for (int i = threadIdx.x; i < n; i += kMergeThreads) {
+        const uint2 me = c[i];
+        if (me.y == 0x7FFFFFFFu) continue;
         int rank = 0;
-        for (int j = 0; j < K; ++j) rank += (sel_key[j] > kk) || (sel_key[j] == kk && sel_idx[j] < ii);
-        idx_out[(size_t)row * K + rank] = ii;
-        val_out[(size_t)row * K + rank] = __uint_as_float((uint32_t)xr[ii] << 16);
+        for (int j = 0; j < n; ++j) {
+            const uint2 o = c[j];
+            rank += (o.x > me.x) || (o.x == me.x && o.y < me.y);
+        }
+        if (rank < K) {
+            idx_out[(size_t)row * K + rank] = (int)me.y;
+            val_out[(size_t)row * K + rank] = __uint_as_float(unsort_key(me.x) << 16);
+        }
     }
 }
 
@@ -176,30 +211,36 @@ __global__ void sample_kernel(const int* idx, const float* val, int width, const
     tokens[row] = pick;
 }
 
-inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, cudaStream_t st, void** args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelExC(&cfg, fn, args);
-}
-
 }  // namespace
 }  // namespace tf
 
 extern "C" {
 
-int tf_topk_rows(const void* x, size_t row_stride, int rows, int vocab, int k, int* idx, float* val, void* stream) {
-    if (rows < 1 || vocab < 1 || k < 1 || k > tf::kMaxK || k > vocab || row_stride < (size_t)vocab) return TF_EINVAL;
+size_t tf_topk_scratch_bytes(int rows, int vocab, int k) {
+    if (rows < 1 || vocab < 1 || k < 1 || k > tf::kMaxK) return 0;
+    return (size_t)rows * tf::slice_count(vocab) * k * sizeof(uint2);
+}
+
+int tf_topk_rows(const void* x, size_t row_stride, int rows, int vocab, int k, int* idx, float* val, void* scratch,
+                 size_t scratch_bytes, void* stream) {
+    if (rows < 1 || rows > 65535 || vocab < 1 || k < 1 || k > tf::kMaxK || k > vocab || row_stride < (size_t)vocab) return TF_EINVAL;
     if (!x || !idx || !val) return TF_EINVAL;
-    void* args[] = {&x, &row_stride, &vocab, &k, &idx, &val};
-    if (tf::launch_pdl((const void*)tf::topk_kernel, dim3(rows), dim3(tf::kThreads), static_cast<cudaStream_t>(stream), args) !=
-        cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
+    const int slices = tf::slice_count(vocab);
+    if (slices > tf::kMaxSlices) return TF_EINVAL;
+    if (!scratch || scratch_bytes < tf_topk_scratch_bytes(rows, vocab, k)) return TF_ESCRATCH;
+    if (reinterpret_cast<uintptr_t>(scratch) & 7) return TF_EALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* a1[] = {&x, &row_stride, &vocab, &k, &scratch};
+    if (tf::launch_pdl((const void*)tf::topk_slice_kernel, dim3(slices, rows), dim3(tf::kSliceThreads), 0, st, a1) != cudaSuccess) {
+        cudaGetLastError();
+        return TF_ECUDA;
+    }
+    int n = slices * k;
+    void* a2[] = {&scratch, &n, &k, &idx, &val};
+    if (tf::launch_pdl((const void*)tf::topk_merge_kernel, dim3(rows), dim3(tf::kMergeThreads), 0, st, a2) != cudaSuccess) {
+        cudaGetLastError();
+        return TF_ECUDA;
+    }
     return TF_OK;
 }
 
@@ -207,7 +248,7 @@ int tf_sample_rows(const int* idx, const float* val, int width, const long long*
                    double temperature, int top_k, double top_p, int* tokens, int rows, void* stream) {
     if (rows < 1 || width < 1 || width > tf::kMaxK || !idx || !val || !positions || !tokens) return TF_EINVAL;
     void* args[] = {&idx, &val, &width, &positions, &seed, &temperature, &top_k, &top_p, &tokens, &rows};
-    if (tf::launch_pdl((const void*)tf::sample_kernel, dim3((rows + 63) / 64), dim3(64), static_cast<cudaStream_t>(stream), args) !=
+    if (tf::launch_pdl((const void*)tf::sample_kernel, dim3((rows + 63) / 64), dim3(64), 0, static_cast<cudaStream_t>(stream), args) !=
         cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
 }

@@ -22,7 +22,7 @@ from . import _lib
 
 MAX_ROWS = 128           # rows one kernel launch accepts (reference: lane_qmm.MAX_ROWS)
 WORKERS = 148            # persistent CTAs the K schedule is cut for (a library constant, not the device's SM count)
-COLUMN_BLOCK = 128       # output columns per column block
+COLUMN_BLOCK = 256       # output columns per column block
 ITEM_TILES = 4           # 64-input k tiles per schedule item, the same for every row count
 
 
@@ -93,7 +93,7 @@ def pack_scales(scales: torch.Tensor, biases: torch.Tensor) -> torch.Tensor:
 
 
 def segments(n: int, k: int) -> list[list[tuple[int, int]]]:
-    """The K schedule: for each 128-column block, the k-tile ranges (64 inputs a tile) whose sums are
+    """The K schedule: for each 256-column block, the k-tile ranges (64 inputs a tile) whose sums are
     formed separately and then added in order. A function of the shape and the worker count only —
     never of the row count."""
 

@@ -1,7 +1,8 @@
 """Top-k over vocabulary rows, exact and deterministic: radix select on bf16 keys.
 
 Mirror of the reference's ``engine/topk.py:130-146`` (``topk_rows``): value descending, ties to the
-lower token id, k <= ``MAX_K``. One CTA per row; a row's result depends on that row alone.
+lower token id, k <= ``MAX_K``. A row is cut into slices (one CTA each) whose candidates a second
+kernel ranks; a row's result depends on that row alone.
 """
 
 from __future__ import annotations
@@ -13,7 +14,7 @@ from . import _lib
 MAX_K = 64
 
 
-def topk_rows(x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+def topk_rows(x: torch.Tensor, k: int, scratch: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """(indices [R, k] int32, values [R, k] float32) of each row's k largest, value desc then id asc."""
 
     _lib.need_cuda(x)
@@ -28,9 +29,13 @@ def topk_rows(x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
         raise ValueError(f"topk_rows: k must be in [1, {MAX_K}] and at most the row length")
     idx = torch.empty((rows, k), dtype=torch.int32, device=x.device)
     val = torch.empty((rows, k), dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    need = lib.tf_topk_scratch_bytes(rows, vocab, k)
+    if scratch is None or scratch.numel() * scratch.element_size() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.load().tf_topk_rows(x2.data_ptr(), x2.stride(0), rows, vocab, k, idx.data_ptr(), val.data_ptr(),
-                                            _lib.stream()), "topk_rows")
+        _lib.check(lib.tf_topk_rows(x2.data_ptr(), x2.stride(0), rows, vocab, k, idx.data_ptr(), val.data_ptr(),
+                                    scratch.data_ptr(), scratch.numel() * scratch.element_size(), _lib.stream()), "topk_rows")
     return idx, val
 
 

@@ -29,7 +29,7 @@ def test_pure_host_entry_points(lib):
     # 16-column x 64-k records of 576 bytes (group 64) / 640 bytes (group 32): 4.5 and 5 bits a weight
     assert lib.tf_qmm_tiled_bytes(17408, 5120, 64) == 17408 * 5120 * 9 // 16
     assert lib.tf_qmm_tiled_bytes(768, 2048, 32) == 768 * 2048 * 5 // 8
-    assert lib.tf_qmm_tiled_bytes(40, 64, 64) == 8 * 576          # columns padded to a 128-column block
+    assert lib.tf_qmm_tiled_bytes(40, 64, 64) == 16 * 576         # columns padded to a 256-column block
     assert lib.tf_packed_bytes(8, 5120, 64) == 80 * 8 * 132 and lib.tf_packed_bytes(9, 2048, 32) == 32 * 16 * 136
     assert lib.tf_qmm_tiled_bytes(16, 100, 64) == 0               # K must be a multiple of 64
     assert lib.tf_qmm_scratch_bytes() > 16384
@@ -55,7 +55,7 @@ def test_k_schedule_is_a_function_of_shape_only():
     from tensorfold_b200 import lane_qmm
 
     segs = lane_qmm.segments(17408, 5120)
-    assert len(segs) == 136
+    assert len(segs) == 68                # 256-column blocks
     for cb in segs:                      # segments tile [0, 80) k tiles in order, no gaps
         assert cb[0][0] == 0 and cb[-1][1] == 80
         assert all(a[1] == b[0] for a, b in zip(cb, cb[1:]))

@@ -223,6 +223,11 @@ def test_topk_rows_matches_lexsort_rule(lib):
     small = torch.randn((3, 100), generator=gen).to(BF)
     idx, _ = topk.topk_rows(small.cuda(), 64)
     assert np.array_equal(idx.cpu().numpy(), O.topk_rows(small.float().numpy(), 64)[0])
+    wide = torch.randn((3, 100011), generator=gen).to(BF)      # rows that start off a 16-byte boundary, several slices
+    view = wide.cuda()[:, 3:100006]
+    idx, val = topk.topk_rows(view, 28)
+    widx, wval = O.topk_rows(wide[:, 3:100006].float().numpy(), 28)
+    assert np.array_equal(idx.cpu().numpy(), widx) and np.array_equal(val.cpu().numpy(), wval)
     one = topk.topk_rows(x[1:2].cuda(), 28)[0]
     assert torch.equal(one, topk.topk_rows(x.cuda(), 28)[0][1:2])
     with pytest.raises(ValueError):

@@ -39,7 +39,7 @@ def qmm(lib):
 def test_tile_roundtrip_keeps_every_bit(qmm, n, k, group):
     _, words, scales, biases = make(n, k, group, seed=n + k)
     q = qmm.tile_weight(words.cuda(), scales.cuda(), biases.cuda(), group)
-    assert q.tiled.numel() == (-(-n // 128)) * 8 * (k // 64) * (576 if group == 64 else 640)
+    assert q.tiled.numel() == (-(-n // 256)) * 16 * (k // 64) * (576 if group == 64 else 640)
     w2, s2, b2 = qmm.untile_weight(q)
     assert torch.equal(w2.cpu(), words) and torch.equal(s2.cpu().view(torch.int16), scales.view(torch.int16))
     assert torch.equal(b2.cpu().view(torch.int16), biases.view(torch.int16))
