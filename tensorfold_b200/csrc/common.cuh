@@ -156,14 +156,13 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- launches ------------------------------------------------------------------------------------
-// Kernels can be launched with programmatic stream serialisation: a kernel may then become resident
-// while its predecessor still runs, do its input-independent work (barrier setup, weight prefetch)
-// and block in pdl_wait() until the predecessor's memory is visible. Measured on B200 this helps a
-// chain of matmuls (about 2 us a launch) but slows a whole forward, where small kernels sit between
-// them, by 20-40%; so it is off unless TF_PDL is set: bit 0 for the small kernels, bit 1 for the matmuls.
-// Without the attribute pdl_wait() and pdl_launch_dependents() do nothing.
+// Kernels are launched with programmatic stream serialisation: a kernel may become resident while
+// its predecessor still runs, do its input-independent work (barrier setup, weight prefetch) and
+// block in pdl_wait() until the predecessor's memory is visible. TF_PDL in the environment narrows it
+// for measurements: bit 0 covers the small kernels, bit 1 the matmuls, 0 is plain stream order (then
+// pdl_wait() and pdl_launch_dependents() do nothing).
 inline int pdl_mode() {
-    static const int mode = [] { const char* e = std::getenv("TF_PDL"); return e ? (e[0] - '0') : 0; }();
+    static const int mode = [] { const char* e = std::getenv("TF_PDL"); return e ? (e[0] - '0') : 3; }();
     return mode;
 }
 inline bool pdl_enabled(bool matmul = false) { return (pdl_mode() & (matmul ? 2 : 1)) != 0; }
