@@ -352,8 +352,8 @@ def main():
                      "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
                      "kernel": "qmm_kernel (4-bit lane matmul)", "launches_per_step": len(mats),
                      "avg_launch_us": 1000.0 * qmm_ms / len(mats), "algorithmic_bytes_per_launch": total_bytes / len(mats),
-                     "traffic": 0.995 * total_bytes / len(mats),
-                     "traffic_note": "dram bytes of one ncu capture (17408x5120, 8 rows: 50.26 MB read for 50.50 MB algorithmic), scaled by units"},
+                     "traffic": 0.996 * total_bytes / len(mats),
+                     "traffic_note": "dram bytes of one ncu capture (17408x5120, 8 rows: 50.28 MB read + 0.03 MB written for 50.50 MB algorithmic), scaled by units"},
         "forward": {"weight_bytes_per_step": weight_bytes, "weight_roofline_ms": weight_bytes / (peak * 1e6),
                     "frac_of_weight_roofline": (weight_bytes / (peak * 1e6)) / (ms / args.steps),
                     "qmm_ms_per_step": qmm_ms, "qmm_share": qmm_ms / (ms / args.steps)},

@@ -12,6 +12,7 @@ works; KV heads are replicated when there are more ranks than KV heads.
 from __future__ import annotations
 
 from dataclasses import replace
+from types import SimpleNamespace
 
 import torch
 
@@ -81,4 +82,76 @@ def sum_rank_partials(partials: torch.Tensor, dtype: torch.dtype = torch.bfloat1
     return acc.to(dtype)
 
 
-__all__ = ["RankGroup", "kv_head_of_rank", "shard_config", "sum_rank_partials"]
+def split_output(q, r0: int, r1: int):
+    """Column-parallel shard of a stored 4-bit projection: whole output rows r0..r1 (packed rows are
+    never cut, so nothing is repacked). Reference: ``distributed.py:32-60`` (``split_output``)."""
+
+    return SimpleNamespace(words=q.words[r0:r1].contiguous(), scales=q.scales[r0:r1].contiguous(),
+                           biases=q.biases[r0:r1].contiguous())
+
+
+def split_input(q, c0: int, c1: int, group: int = 64):
+    """Row-parallel shard: inputs c0..c1, whole groups (words ``[:, c0/8:c1/8]``, scales and biases
+    ``[:, c0/group:c1/group]``). Reference: ``distributed.py:62-98`` (``split_input``)."""
+
+    if c0 % group or c1 % group:
+        raise ValueError("row-parallel shards must be whole input groups")
+    return SimpleNamespace(words=q.words[:, c0 // 8:c1 // 8].contiguous(), scales=q.scales[:, c0 // group:c1 // group].contiguous(),
+                           biases=q.biases[:, c0 // group:c1 // group].contiguous())
+
+
+def _cat(parts):
+    return SimpleNamespace(words=torch.cat([p.words for p in parts]), scales=torch.cat([p.scales for p in parts]),
+                           biases=torch.cat([p.biases for p in parts]))
+
+
+def split_model(model: dict, rank: int, world: int) -> dict:
+    """The tensor-parallel shard of a stored model (the dict ``forward.load_weights`` reads): heads and
+    MLP width by output rows, output/down projections by input groups, vocabulary rows for the head;
+    norms and the embedding are replicated. Reference: ``distributed.py:100-171`` (``split_layer``,
+    ``split_weights``)."""
+
+    cfg = model["config"]
+    if world == 1:
+        return model
+    sc = shard_config(cfg, rank, world)
+    g = cfg.group
+    kd, vd = cfg.k_heads * cfg.dk, cfg.v_heads * cfg.dv
+    kdl, vdl = sc.k_heads * cfg.dk, sc.v_heads * cfg.dv
+    il = sc.intermediate
+    kv0 = kv_head_of_rank(cfg, rank, world).start
+    hd = cfg.head_dim
+    layers = []
+    for src in model["layers"]:
+        out = {"linear": src["linear"], "input_norm": src["input_norm"], "post_norm": src["post_norm"],
+               "gate": split_output(src["gate"], rank * il, (rank + 1) * il), "up": split_output(src["up"], rank * il, (rank + 1) * il),
+               "down": split_input(src["down"], rank * il, (rank + 1) * il, g)}
+        if src["linear"]:
+            def seg(t):
+                return (t[rank * kdl:(rank + 1) * kdl], t[kd + rank * kdl:kd + (rank + 1) * kdl],
+                        t[2 * kd + rank * vdl:2 * kd + (rank + 1) * vdl])
+            qkv = src["qkv"]
+            out["qkv"] = _cat([split_output(qkv, rank * kdl, (rank + 1) * kdl), split_output(qkv, kd + rank * kdl, kd + (rank + 1) * kdl),
+                               split_output(qkv, 2 * kd + rank * vdl, 2 * kd + (rank + 1) * vdl)])
+            out["z"] = split_output(src["z"], rank * vdl, (rank + 1) * vdl)
+            out["b"] = split_output(src["b"], rank * sc.v_heads, (rank + 1) * sc.v_heads)
+            out["a"] = split_output(src["a"], rank * sc.v_heads, (rank + 1) * sc.v_heads)
+            out["out"] = split_input(src["out"], rank * vdl, (rank + 1) * vdl, g)
+            out["conv"] = torch.cat(seg(src["conv"]))
+            out["A_log"] = src["A_log"][rank * sc.v_heads:(rank + 1) * sc.v_heads]
+            out["dt_bias"] = src["dt_bias"][rank * sc.v_heads:(rank + 1) * sc.v_heads]
+            out["norm"] = src["norm"]
+        else:
+            h0, h1 = rank * sc.heads, (rank + 1) * sc.heads
+            out["q"] = split_output(src["q"], h0 * 2 * hd, h1 * 2 * hd)            # per-head [q_h ; gate_h] blocks
+            out["k"] = split_output(src["k"], kv0 * hd, (kv0 + sc.kv_heads) * hd)
+            out["v"] = split_output(src["v"], kv0 * hd, (kv0 + sc.kv_heads) * hd)
+            out["o"] = split_input(src["o"], h0 * hd, h1 * hd, g)
+            out["q_norm"], out["k_norm"] = src["q_norm"], src["k_norm"]
+        layers.append(out)
+    vl = sc.vocab
+    return {"config": sc, "layers": layers, "embed": model["embed"], "norm": model["norm"],
+            "head": split_output(model["head"], rank * vl, (rank + 1) * vl)}
+
+
+__all__ = ["RankGroup", "kv_head_of_rank", "shard_config", "split_input", "split_model", "split_output", "sum_rank_partials"]

@@ -101,3 +101,39 @@ def test_split_vocabulary_candidates_contain_the_whole_vocabulary_draw():
     wi, wv = O.topk_rows(logits, 28)
     assert np.array_equal(midx.numpy(), wi) and np.array_equal(mval.numpy(), wv)
     assert S.choose_rows(mval.numpy(), midx.numpy(), positions, s) == whole
+
+
+def test_split_model_shards_reassemble_into_the_stored_model():
+    """Column-parallel shards are whole output rows, row-parallel shards whole input groups: stacking
+    them back gives the stored arrays (reference: tests/cuda/test_qwen27_tp.py partition checks)."""
+
+    from oracle import lane_oracle as O
+    from tensorfold_b200 import distributed as D
+
+    cfg = O.Config(hidden=512, intermediate=1024, layers=4, heads=8, kv_heads=2, head_dim=128, vocab=1024, k_heads=8,
+                   v_heads=16, dk=128, dv=128)
+    model = O.random_model(cfg, 5)
+    for world in (2, 4, 8):
+        shards = [D.split_model(model, r, world) for r in range(world)]
+        lin, att = model["layers"][0], model["layers"][3]
+        assert lin["linear"] and not att["linear"]
+        for name in ("gate", "up", "z", "b", "a"):
+            assert torch.equal(torch.cat([s["layers"][0][name].words for s in shards]), lin[name].words)
+            assert torch.equal(torch.cat([s["layers"][0][name].scales for s in shards]), lin[name].scales)
+        for name in ("down", "out"):
+            assert torch.equal(torch.cat([s["layers"][0][name].words for s in shards], 1), lin[name].words)
+            assert torch.equal(torch.cat([s["layers"][0][name].biases for s in shards], 1), lin[name].biases)
+        kd = cfg.k_heads * cfg.dk
+        kdl = kd // world
+        q_rows = torch.cat([s["layers"][0]["qkv"].words[:kdl] for s in shards])
+        assert torch.equal(q_rows, lin["qkv"].words[:kd])
+        assert torch.equal(torch.cat([s["layers"][0]["conv"][:kdl] for s in shards]), lin["conv"][:kd])
+        assert torch.equal(torch.cat([s["layers"][3]["q"].words for s in shards]), att["q"].words)
+        assert torch.equal(torch.cat([s["layers"][3]["o"].words for s in shards], 1), att["o"].words)
+        # KV heads: split while they last, then one replicated head per rank
+        per = max(1, cfg.kv_heads // world)
+        for r, s in enumerate(shards):
+            h0 = D.kv_head_of_rank(cfg, r, world).start
+            assert torch.equal(s["layers"][3]["k"].words, att["k"].words[h0 * 128:(h0 + per) * 128])
+            assert s["config"].kv_heads == per and s["config"].vocab == cfg.vocab // world
+        assert torch.equal(torch.cat([s["head"].words for s in shards]), model["head"].words)

@@ -1,0 +1,32 @@
+"""Tensor parallelism on real GPUs: one process per GPU under torchrun (NCCL). Skipped with fewer than
+two GPUs; the host-side rules (ordered sum, candidate merge, sharding) are covered on CPU with gloo in
+test_distributed_cpu.py."""
+
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_window_rows_equal_serial_steps_under_tp(lib, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29400 + world), str(ROOT / "tests" / "tp_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = re.search(r"TP_RESULT world=(\d+) window_equals_serial=(\d) head_ok=(\d) cos_vs_one_gpu=([0-9.]+)", out.stdout)
+    assert m, out.stdout[-2000:]
+    assert int(m.group(1)) == world
+    assert m.group(2) == "1", "window rows differ from the same ranks' serial decode"
+    assert m.group(3) == "1", "vocabulary-split draw differs from the whole-vocabulary draw"
+    assert float(m.group(4)) > 0.999          # the reference's cross-world bound (tests/cuda/test_flashnext_tp.py:218-227)
