@@ -340,6 +340,9 @@ def main():
     weight_bytes = sum(q.n * q.k // 2 + q.n * (q.k // q.group) * 4 for q in mats)
     _lib.status(dev).raise_if_set()
     if rank != 0:
+        # every rank leaves the process group together: a rank that exits alone leaves the others waiting
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
         return
     line = {
         "metric": "lane-verify rows/sec", "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
@@ -360,8 +363,9 @@ def main():
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, rows)
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
     if world > 1:
+        torch.distributed.barrier()
         torch.distributed.destroy_process_group()
 
 
