@@ -173,6 +173,20 @@ def only_qmm(args, dev):
                       "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
 
 
+def leave_group():
+    """Every rank leaves the process group together; a timer ends the process if the teardown itself
+    stalls (the result line is already printed by then)."""
+
+    import torch
+
+    guard = threading.Timer(60.0, lambda: os._exit(0))
+    guard.daemon = True
+    guard.start()
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+    guard.cancel()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,9 +354,7 @@ def main():
     weight_bytes = sum(q.n * q.k // 2 + q.n * (q.k // q.group) * 4 for q in mats)
     _lib.status(dev).raise_if_set()
     if rank != 0:
-        # every rank leaves the process group together: a rank that exits alone leaves the others waiting
-        torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
+        leave_group()       # a rank that exits alone leaves the others waiting
         return
     line = {
         "metric": "lane-verify rows/sec", "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
@@ -365,8 +377,7 @@ def main():
         line["cpu_baseline"] = cpu_reference(args, rows)
     print(json.dumps(line), flush=True)
     if world > 1:
-        torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
+        leave_group()
 
 
 if __name__ == "__main__":
