@@ -64,6 +64,17 @@ size_t tf_packed_bytes(int M, int K, int group);
 int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
            int K, int group, int flags, int* status, void* stream);
 
+/* Grouped form for mixture-of-experts layers: up to max_probs independent problems of 8 rows each in
+ * one launch. Problem p multiplies its packed rows (x_packed + p * tf_packed_bytes(8, K, group)) with
+ * the weight of expert prob_expert[p] (w_tiled + e * tf_qmm_tiled_bytes(N, K, group): the experts'
+ * tiled weights stacked) into y + p * 8 * N elements. The number of live problems is read on the
+ * device from prob_count[0] (clamped to max_probs), so a captured step serves any routing. A row's
+ * result is that of tf_qmm on the same row and weight: the arithmetic is the 8-row bucket's always.
+ * Replaces: families/qwen4_exp/cuda/qmm.py:421-602 (Experts, Group, moe_gateup, moe_down). */
+int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count, int max_probs,
+                   void* y, void* scratch, size_t scratch_bytes, int N, int K, int group, int flags, int* status,
+                   void* stream);
+
 /* Row-major bf16 rows x [M, K] -> packed rows with their group sums; when xs is not NULL the sums
  * are also written as [M, K/group] fp32. A group's sum is formed in eights: eight (group 64) or four
  * (group 32) sequential 8-element sums combined by a pairwise tree.
@@ -238,6 +249,36 @@ int tf_lane_attention_paged_static(const void* q, const void* k_new, const void*
 int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, void* k_pages, void* v_pages,
                  long long pages_stride, const int* page_table, int max_pages, const int* seq_lens, const int* seq_start,
                  const int* keep, int n_seqs, int layers, int kv_heads, int head_dim, void* stream);
+
+/* ---- mixture-of-experts block -------------------------------------------------------------------
+ * Replaces: families/qwen4_exp/cuda/moe.py:42-163 (router, select, MoEBuffers, moe) and the combine of
+ * families/qwen4_exp/cuda/glue.py:85-91. The expert projections run through tf_qmm_grouped.
+ *
+ * tf_moe_router: logits[r, e] = fp32 x[r] . router[e] for e < experts_total (the routed experts' rows,
+ *   then optionally the shared expert's gate row); bf16 inputs, D a multiple of 256, one fixed
+ *   summation order per D.
+ * tf_moe_select: per row the top_k routed experts by (logit descending, id ascending) with weights
+ *   bf16(exp(l_k - l_0) / sum) and, when experts_total = experts + 1, the shared expert (id `experts`)
+ *   as the last slot with weight bf16(sigmoid(bf16(gate logit))). pick int32, wts fp32 [rows, slots].
+ * tf_moe_group: the window's problem list for tf_qmm_grouped: distinct experts in ascending id, each
+ *   cut into problems of up to 8 members in row order. prob_expert [max_probs], prob_count [1],
+ *   prob_rows [max_probs, 8] (row * 32 + slot, or -1), pair_loc [rows, slots] = problem * 8 + place.
+ *   max_probs from tf_moe_max_problems. rows <= 128.
+ * tf_moe_pack: problem p's member rows of x [rows, K], packed for the matmul (absent members zero).
+ * tf_moe_act: compact gate/up results [problem, 8, 2 I] bf16 -> bf16(silu(gate) * up), packed for the
+ *   down projection of the same problems.
+ * tf_moe_combine: out[r] = bf16(sum over slots, in slot order, of wts[r, k] * y[pair_loc[r, k]]) with
+ *   y the compact fp32 down results [problem * 8 + place, D]; fma, one rounding. */
+int tf_moe_max_problems(int rows, int slots, int experts_total);
+int tf_moe_router(const void* x, size_t x_stride, const void* router, float* logits, int rows, int D, int experts_total,
+                  void* stream);
+int tf_moe_select(const float* logits, int rows, int experts_total, int experts, int top_k, int* pick, float* wts, void* stream);
+int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int max_probs, int* prob_expert, int* prob_count,
+                 int* prob_rows, int* pair_loc, void* stream);
+int tf_moe_pack(const void* x, size_t x_stride, const int* prob_rows, const int* prob_count, int max_probs, void* x_packed, int K,
+                int group, void* stream);
+int tf_moe_act(const void* gate_up, const int* prob_count, int max_probs, void* act_packed, int I, int group, void* stream);
+int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* stream);
 
 /* ---- exact top-k and keyed sampling --------------------------------------------------------------
  * Each row's k largest bf16 logits (k <= 64), ordered by value descending then id ascending; ties at

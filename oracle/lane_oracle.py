@@ -113,6 +113,69 @@ def qmm_ordered(x: torch.Tensor, words, scales, biases, group: int | None = None
 
 
 # ------------------------------------------------------------------------------------------------
+# mixture-of-experts block (``families/qwen4_exp/cuda/moe.py``, ``qmm.py:421-602``, ``glue.py:85-91``)
+# ------------------------------------------------------------------------------------------------
+
+def moe_router(x: torch.Tensor, router_rows: torch.Tensor) -> torch.Tensor:
+    """fp32 logits = bf16 x . bf16 rows (``moe.py:25-41``)."""
+
+    return x.float() @ router_rows.float().T
+
+
+def moe_select(logits: torch.Tensor, experts: int, top_k: int, shared: bool):
+    """Per row: the top_k routed experts by (logit descending, id ascending), weights
+    bf16(exp(l_k - l_0) / sum) with the sum in slot order, then the shared expert (id ``experts``) with
+    weight bf16(sigmoid(bf16(gate logit))) (``moe.py:64-97``). Returns (pick int32, wts fp32)."""
+
+    rows = logits.shape[0]
+    slots = top_k + (1 if shared else 0)
+    pick = torch.zeros((rows, slots), dtype=torch.int32)
+    wts = torch.zeros((rows, slots), dtype=torch.float32)
+    for r in range(rows):
+        v = logits[r, :experts].clone()
+        chosen, exs = [], []
+        top = v.max()
+        for _ in range(top_k):
+            m = v.max()
+            idx = int((v == m).nonzero()[0])
+            chosen.append(idx)
+            exs.append(torch.exp(m - top))
+            v[idx] = float("-inf")
+        total = torch.zeros((), dtype=torch.float32)
+        for e in exs:
+            total = total + e
+        for k in range(top_k):
+            pick[r, k] = chosen[k]
+            wts[r, k] = (exs[k] / total).to(BF16).float()
+        if shared:
+            sg = logits[r, experts].to(BF16).float()
+            pick[r, top_k] = experts
+            wts[r, top_k] = (1.0 / (1.0 + torch.exp(-sg))).to(BF16).float()
+    return pick, wts
+
+
+def moe_experts(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor, gates, ups, downs, group: int = 32) -> torch.Tensor:
+    """Every (row, expert) pair alone: act = bf16(silu(bf16 gate) * bf16 up), y = fp32 down(act); a row's
+    result is bf16(sum_k w_k y_k) in slot order (``qmm.py:517-526``, ``glue.py:85-91``)."""
+
+    rows, slots = pick.shape
+    dq = {}
+    out = torch.zeros((rows, x.shape[1]), dtype=torch.float32)
+    for r in range(rows):
+        acc = torch.zeros(x.shape[1], dtype=torch.float32)
+        for k in range(slots):
+            e = int(pick[r, k])
+            if e not in dq:
+                dq[e] = tuple(dequantize(q.words, q.scales, q.biases, group) for q in (gates[e], ups[e], downs[e]))
+            wg, wu, wd = dq[e]
+            xr = x[r:r + 1].float()
+            act = swiglu((xr @ wg.T).to(BF16), (xr @ wu.T).to(BF16))
+            acc = acc + wts[r, k] * (act.float() @ wd.T)[0]
+        out[r] = acc
+    return out.to(BF16)
+
+
+# ------------------------------------------------------------------------------------------------
 # glue (``families/qwen3_5/cuda/glue.py``; fp32 forms as in ``reference.py``)
 # ------------------------------------------------------------------------------------------------
 

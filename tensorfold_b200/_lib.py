@@ -28,6 +28,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p]),
+    "tf_qmm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_int, c_int,
+                               c_int, c_int, c_void_p, c_void_p]),
     "tf_pack_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -66,6 +68,13 @@ SIGNATURES: dict[str, tuple] = {
                                                c_float, c_void_p]),
     "tf_kv_commit": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_moe_max_problems": (c_int, [c_int, c_int, c_int]),
+    "tf_moe_router": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_moe_select": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "tf_moe_group": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tf_moe_pack": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "tf_moe_act": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "tf_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_topk_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tf_sample_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_ulonglong, c_double, c_int, c_double, c_void_p,
@@ -75,7 +84,7 @@ SIGNATURES: dict[str, tuple] = {
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
 _NO_LAUNCH = {"tf_version", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes"}
+              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems"}
 
 
 def launch_count() -> int:

@@ -35,12 +35,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return a | (b << 16);
 }
 
+// ---- eight bf16 values in a 16-byte chunk ------------------------------------------------------------
+__device__ __forceinline__ void unpack8(uint4 v, float (&f)[8]) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = bf16_lo(u[i]); f[2 * i + 1] = bf16_hi(u[i]); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
 // ---- packed activations -------------------------------------------------------------------------
 // The lane matmul reads its input rows "packed": per k tile (64 inputs), Mp = M rounded up to its row
 // bucket (8, 16, 32, 64 or 128) rows of 128 bytes each (16-byte chunk c of row r stored at chunk
 // c ^ 4*(r&1); rows past M are zero), followed by the tile's group sums as [groups in the tile][Mp] fp32. Every kernel that produces matmul input writes this
 // form directly with the two helpers below, so the sums are formed the same way everywhere.
 __host__ __device__ constexpr int tf_padded_rows(int m) { return m <= 8 ? 8 : m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+__host__ __device__ constexpr size_t tf_packed_size(int mp, int k, int group) { return (size_t)(k / 64) * mp * (128 + 4 * (64 / group)); }
 
 // fp32 sum of a G-input group: each lane adds its 8 contiguous bf16 values in order, then the G/8
 // lanes holding the group combine in a pairwise tree. Call with whole warps; every lane of the

@@ -17,15 +17,6 @@
 namespace tf {
 namespace {
 
-__device__ __forceinline__ void unpack8(uint4 v, float (&f)[8]) {
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { f[2 * i] = bf16_lo(u[i]); f[2 * i + 1] = bf16_hi(u[i]); }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-    return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-}
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float inv_rms(float sumsq, int n, float eps) { return 1.0f / sqrtf(sumsq / (float)n + eps); }
 
 // Sum over the whole CTA in a fixed order: xor-tree inside each warp, then the warp totals in warp

@@ -1,0 +1,295 @@
+// Mixture-of-experts block around the grouped lane matmul: router logits, per-row selection, the
+// window's problem list, gather/pack of expert inputs, the expert activation, and the slot-ordered
+// combine.
+//
+// Every step treats a row on its own: the router is one fixed-order fp32 dot per (row, expert), the
+// selection looks at the row's logits only, an expert's rows are multiplied in 8-row problems whose
+// arithmetic does not depend on the companions (tf_qmm_grouped), and the combine adds a row's slots in
+// slot order. So a row of a window has the bits of the same row routed and computed alone.
+//
+// Problem list: the distinct experts of a window in ascending id, each cut into problems of up to 8
+// members (a member = one (row, slot) pair, in row order). prob_expert[p] names the expert,
+// prob_rows[p][j] the member (row * 32 + slot, or -1), pair_loc[row][slot] = p * 8 + j says where the
+// pair's results live in the compact [problem][8][...] buffers. The shared expert is expert id E and
+// rides as the last slot of every row.
+
+#include "common.cuh"
+
+namespace tf {
+namespace {
+
+constexpr int kMaxExperts = 1023;      // routed experts + the shared one fit one CTA of 1024 threads
+constexpr int kMaxSlots = 32;          // member code = row * 32 + slot
+
+// ---- router: logits[r, e] = fp32 x[r] . w[e] ------------------------------------------------------
+// One warp per (expert, block of 8 rows). Lane l owns inputs 8l..8l+7 of every 256-input step and adds
+// them in order with fma; the 32 lane sums combine in a pairwise tree. Fixed by D alone.
+__global__ void __launch_bounds__(128) moe_router_kernel(const __nv_bfloat16* x, size_t x_stride, const __nv_bfloat16* w, float* out,
+                                                         int R, int D, int NE) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 4 + warp, r0 = blockIdx.y * 8;
+    if (e >= NE) return;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const int rows = min(8, R - r0);
+    for (int k = lane * 8; k < D; k += 256) {
+        float wv[8];
+        unpack8(*reinterpret_cast<const uint4*>(w + (size_t)e * D + k), wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < rows) {
+                float xv[8];
+                unpack8(*reinterpret_cast<const uint4*>(x + (size_t)(r0 + i) * x_stride + k), xv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i] = __fmaf_rn(xv[j], wv[j], acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float v = acc[i];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && i < rows) out[(size_t)(r0 + i) * NE + e] = v;
+    }
+}
+
+// ---- selection: one warp per row ------------------------------------------------------------------
+// top_k experts by (logit descending, id ascending); weights bf16(exp(l_k - l_0) / sum), the sum in
+// slot order; then the shared expert (id E) as slot top_k with weight bf16(sigmoid(bf16(its logit))).
+__global__ void __launch_bounds__(32) moe_select_kernel(const float* logits, int NE, int E, int top_k, int* pick, float* wts) {
+    __shared__ float v[kMaxExperts + 1];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, lane = threadIdx.x, slots = top_k + (NE > E ? 1 : 0);
+    for (int i = lane; i < E; i += 32) v[i] = logits[(size_t)r * NE + i];
+    __syncwarp();
+    float top = 0.f, total = 0.f, mine = 0.f;
+    int my_pick = 0;
+    for (int k = 0; k < top_k; ++k) {
+        float best = -INFINITY;
+        int at = 0x7FFFFFFF;
+        for (int i = lane; i < E; i += 32) {
+            const float c = v[i];
+            if (c > best || (c == best && i < at)) { best = c; at = i; }     // ascending i: the first maximum
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (k == 0) top = best;
+        const float ex = expf(best - top);
+        total += ex;
+        if (lane == k) { mine = ex; my_pick = at; }
+        if (lane == 0 && at < E) v[at] = -INFINITY;
+        __syncwarp();
+    }
+    if (lane < top_k) {
+        pick[(size_t)r * slots + lane] = my_pick;
+        wts[(size_t)r * slots + lane] = bf2f(f2bf(mine / total));
+    }
+    if (lane == 0 && NE > E) {
+        const float sg = bf2f(f2bf(logits[(size_t)r * NE + E]));
+        pick[(size_t)r * slots + top_k] = E;
+        wts[(size_t)r * slots + top_k] = bf2f(f2bf(1.0f / (1.0f + expf(-sg))));
+    }
+}
+
+// ---- problem list: one CTA, one thread per expert id ----------------------------------------------
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R, int slots, int NE, int max_probs, int* prob_expert,
+                                                         int* prob_count, int* prob_rows, int* pair_loc) {
+    extern __shared__ int sh_pick[];             // R * slots picks
+    __shared__ int warp_tot[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+    const int pairs = R * slots;
+    for (int i = e; i < pairs; i += 1024) sh_pick[i] = pick[i];
+    __syncthreads();
+    int cnt = 0;
+    if (e < NE)
+        for (int i = 0; i < pairs; ++i) cnt += sh_pick[i] == e;
+    const int mine = (cnt + 7) >> 3;             // problems of this expert
+    // exclusive prefix sum over expert ids (fixed order)
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_tot[lane], winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_tot[lane] = winc - w;
+        if (lane == 31) warp_tot[32] = winc;
+    }
+    __syncthreads();
+    const int base = warp_tot[warp] + inc - mine, total = min(warp_tot[32], max_probs);
+    if (e == 0) prob_count[0] = total;
+    if (e < NE && cnt > 0) {
+        int j = 0;
+        for (int i = 0; i < pairs; ++i) {
+            if (sh_pick[i] != e) continue;
+            const int p = base + (j >> 3);
+            if (p < max_probs) {
+                const int row = i / slots, slot = i - row * slots;
+                prob_rows[p * 8 + (j & 7)] = row * kMaxSlots + slot;
+                pair_loc[i] = p * 8 + (j & 7);
+                if ((j & 7) == 0) prob_expert[p] = e;
+            }
+            ++j;
+        }
+        for (; j & 7; ++j) {
+            const int p = base + (j >> 3);
+            if (p < max_probs) prob_rows[p * 8 + (j & 7)] = -1;
+        }
+    }
+}
+
+// ---- gather + pack: problem p's 8 input rows in the matmul's packed form ---------------------------
+// A member reads its window row of x [R, K]; absent members are zero rows.
+template <int G>
+__global__ void moe_pack_kernel(const __nv_bfloat16* x, size_t x_stride, const int* prob_rows, const int* prob_count, int max_probs,
+                                uint8_t* xp, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.y;
+    if (p >= min(prob_count[0], max_probs)) return;
+    const int id = blockIdx.x * blockDim.x + threadIdx.x;
+    const int chunks = 8 * (K >> 3);
+    const int j = id / (K >> 3), c = id - j * (K >> 3);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (id < chunks) {
+        const int code = prob_rows[p * 8 + j];
+        if (code >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(code / kMaxSlots) * x_stride + 8 * c);
+    }
+    const float s = group_sum8<G>(v);
+    if (id >= chunks) return;
+    packed_store<G>(xp + (size_t)p * tf_packed_size(8, K, G), 8, j, c, v, s);
+}
+
+// ---- expert activation: act = bf16(silu(gate) * up) of problem p's rows, packed for the down matmul ---
+template <int G>
+__global__ void moe_act_kernel(const __nv_bfloat16* gate_up, const int* prob_count, int max_probs, uint8_t* act_packed, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.y;
+    if (p >= min(prob_count[0], max_probs)) return;
+    const int id = blockIdx.x * blockDim.x + threadIdx.x;
+    const int chunks = 8 * (I >> 3);
+    const int j = id / (I >> 3), c = id - j * (I >> 3);
+    uint4 ov = make_uint4(0, 0, 0, 0);
+    if (id < chunks) {
+        const __nv_bfloat16* row = gate_up + ((size_t)p * 8 + j) * 2 * I;
+        float g[8], u[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(row + 8 * c), g);
+        unpack8(*reinterpret_cast<const uint4*>(row + I + 8 * c), u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = g[i] * sigmoidf_(g[i]) * u[i];
+        ov = pack8(o);
+    }
+    const float s = group_sum8<G>(ov);
+    if (id >= chunks) return;
+    packed_store<G>(act_packed + (size_t)p * tf_packed_size(8, I, G), 8, j, c, ov, s);
+}
+
+// ---- combine: out[r] = bf16( sum over slots in order of w[r,k] * y[pair (r,k)] ) --------------------
+__global__ void moe_combine_kernel(const float* y, const int* pair_loc, const float* wts, int slots, __nv_bfloat16* out, int R, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= (D >> 2) || r >= R) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < slots; ++k) {
+        const float w = wts[(size_t)r * slots + k];
+        const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pair_loc[r * slots + k] * D + 4 * c);
+        acc.x = __fmaf_rn(w, v.x, acc.x);
+        acc.y = __fmaf_rn(w, v.y, acc.y);
+        acc.z = __fmaf_rn(w, v.z, acc.z);
+        acc.w = __fmaf_rn(w, v.w, acc.w);
+    }
+    __nv_bfloat16* o = out + (size_t)r * D + 4 * c;
+    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc.x, acc.y);
+    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+}
+
+}  // namespace
+}  // namespace tf
+
+extern "C" {
+
+int tf_moe_max_problems(int rows, int slots, int experts_total) {
+    if (rows < 1 || slots < 1 || experts_total < 1) return 0;
+    const int pairs = rows * slots;
+    return (experts_total < pairs ? experts_total : pairs) + pairs / 8;
+}
+
+int tf_moe_router(const void* x, size_t x_stride, const void* router, float* logits, int rows, int D, int experts_total,
+                  void* stream) {
+    if (rows < 1 || D < 256 || D % 256 || experts_total < 1 || !x || !router || !logits || x_stride < (size_t)D) return TF_EINVAL;
+    if (((uintptr_t)x | (uintptr_t)router | (x_stride * 2)) & 15) return TF_EALIGN;
+    void* args[] = {&x, &x_stride, &router, &logits, &rows, &D, &experts_total};
+    return tf::launch_pdl((const void*)tf::moe_router_kernel, dim3((experts_total + 3) / 4, (rows + 7) / 8), dim3(128), 0,
+                          static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_select(const float* logits, int rows, int experts_total, int experts, int top_k, int* pick, float* wts, void* stream) {
+    if (rows < 1 || experts < 1 || experts > tf::kMaxExperts || top_k < 1 || top_k > experts || top_k + 1 > tf::kMaxSlots) return TF_EINVAL;
+    if (experts_total != experts && experts_total != experts + 1) return TF_EINVAL;
+    if (!logits || !pick || !wts) return TF_EINVAL;
+    void* args[] = {&logits, &experts_total, &experts, &top_k, &pick, &wts};
+    return tf::launch_pdl((const void*)tf::moe_select_kernel, dim3(rows), dim3(32), 0, static_cast<cudaStream_t>(stream), args) ==
+                   cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int max_probs, int* prob_expert, int* prob_count,
+                 int* prob_rows, int* pair_loc, void* stream) {
+    if (rows < 1 || rows > 128 || slots < 1 || slots > tf::kMaxSlots || experts_total < 1 || experts_total > tf::kMaxExperts + 1) return TF_EINVAL;
+    if (max_probs < 1 || !pick || !prob_expert || !prob_count || !prob_rows || !pair_loc) return TF_EINVAL;
+    size_t smem = (size_t)rows * slots * sizeof(int);
+    void* args[] = {&pick, &rows, &slots, &experts_total, &max_probs, &prob_expert, &prob_count, &prob_rows, &pair_loc};
+    return tf::launch_pdl((const void*)tf::moe_group_kernel, dim3(1), dim3(1024), smem, static_cast<cudaStream_t>(stream), args) ==
+                   cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_pack(const void* x, size_t x_stride, const int* prob_rows, const int* prob_count, int max_probs, void* x_packed, int K,
+                int group, void* stream) {
+    if (max_probs < 1 || max_probs > 65535 || K < 64 || K % 64 || (group != 64 && group != 32)) return TF_EINVAL;
+    if (!x || !prob_rows || !prob_count || !x_packed || x_stride < (size_t)K) return TF_EINVAL;
+    if (((uintptr_t)x | (uintptr_t)x_packed | (x_stride * 2)) & 15) return TF_EALIGN;
+    void* args[] = {&x, &x_stride, &prob_rows, &prob_count, &max_probs, &x_packed, &K};
+    const void* fn = group == 64 ? (const void*)tf::moe_pack_kernel<64> : (const void*)tf::moe_pack_kernel<32>;
+    return tf::launch_pdl(fn, dim3((K + 255) / 256, max_probs), dim3(256), 0, static_cast<cudaStream_t>(stream), args) == cudaSuccess
+               ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_act(const void* gate_up, const int* prob_count, int max_probs, void* act_packed, int I, int group, void* stream) {
+    if (max_probs < 1 || max_probs > 65535 || I < 64 || I % 64 || (group != 64 && group != 32)) return TF_EINVAL;
+    if (!gate_up || !prob_count || !act_packed) return TF_EINVAL;
+    if (((uintptr_t)gate_up | (uintptr_t)act_packed) & 15) return TF_EALIGN;
+    void* args[] = {&gate_up, &prob_count, &max_probs, &act_packed, &I};
+    const void* fn = group == 64 ? (const void*)tf::moe_act_kernel<64> : (const void*)tf::moe_act_kernel<32>;
+    return tf::launch_pdl(fn, dim3((I + 255) / 256, max_probs), dim3(256), 0, static_cast<cudaStream_t>(stream), args) == cudaSuccess
+               ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* stream) {
+    if (rows < 1 || rows > 65535 || slots < 1 || D < 8 || D % 8 || !y || !pair_loc || !wts || !out) return TF_EINVAL;
+    if (((uintptr_t)y | (uintptr_t)out) & 15) return TF_EALIGN;
+    void* args[] = {&y, &pair_loc, &wts, &slots, &out, &rows, &D};
+    return tf::launch_pdl((const void*)tf::moe_combine_kernel, dim3((D / 4 + 255) / 256, rows), dim3(256), 0,
+                          static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+}  // extern "C"

@@ -71,6 +71,13 @@ struct Args {
     int* status;
     int M, N, K;
     int f32_out;
+    // grouped form (MoE experts): `max_probs` problems of 8 rows each, problem p multiplying its own
+    // packed rows (xp + p * xp_stride) with the weight of expert prob_expert[p] (w + e * w_stride)
+    // into y + p * y_stride elements; the live count is read on the device. nullptr: one problem.
+    const int* prob_expert;
+    const int* prob_count;
+    int max_probs;
+    long long w_stride, xp_stride, y_stride;
 };
 
 // Work items (column block, group of kItemTiles k tiles) are split evenly over kWorkers CTAs.
@@ -91,10 +98,11 @@ __device__ __forceinline__ void group_sync() {
 }
 
 template <int NT>
-__device__ void finish_segment(const Args& a, int cb, int SPB, int total, int tid, int* list) {
+__device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total, int tid, int* list) {
     __threadfence();
     group_sync<NT>();
-    const int cb_begin = cb * SPB;
+    const int cb_begin = gb * SPB;
+    const int prob = gb / CB, cb = gb - prob * CB;
     if (tid == 0) {
         const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
         int nseg = 0;
@@ -104,7 +112,7 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int ti
             list[nseg++] = 2 * o + (ob < cb_begin ? 1 : 0);      // its slot, in k order
         }
         list[kWorkers] = nseg;
-        list[kWorkers + 1] = atomicAdd(a.counters + cb, 1);
+        list[kWorkers + 1] = atomicAdd(a.counters + gb, 1);
     }
     group_sync<NT>();
     const int nseg = list[kWorkers];
@@ -149,13 +157,13 @@ __device__ void finish_segment(const Args& a, int cb, int SPB, int total, int ti
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 if (col + i >= a.N) break;
-                const size_t at = (size_t)row * a.N + col + i;
+                const size_t at = (size_t)prob * a.y_stride + (size_t)row * a.N + col + i;
                 if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = e[i];
                 else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(e[i]);
             }
         }
     }
-    if (tid == 0) a.counters[cb] = 0;      // leave the counters zero for the next call (every reader is past its ticket)
+    if (tid == 0) a.counters[gb] = 0;      // leave the counters zero for the next call (every reader is past its ticket)
 }
 
 template <int G, int MB, int KTS, int STAGES>
@@ -168,7 +176,10 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     const int KT = a.K >> 6;                              // k tiles
     const int CB = (a.N + kCols - 1) / kCols;             // column blocks
     const int SPB = (KT + kItemTiles - 1) / kItemTiles;   // schedule items per column block
-    const int total = CB * SPB;
+    const bool multi = a.prob_expert != nullptr;
+    if (multi) pdl_wait();                                // the problem list is the previous kernel's output
+    const int probs = multi ? min(*a.prob_count, a.max_probs) : 1;
+    const int total = probs * CB * SPB;                   // "column block" below: (problem, column block) pairs
     const int begin = range_begin(blockIdx.x, total), end = range_begin(blockIdx.x + 1, total);
 
     uint8_t* stage0 = smem;
@@ -199,9 +210,12 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
         if (lane == 0 && begin < end) {
             int s = 0, issued = 0;
             uint32_t phase = 1;
-            int cb = cb_first, st = begin - cb * SPB;
+            int gb = cb_first, st = begin - gb * SPB;
+            int prob = gb / CB, cb = gb - prob * CB;
+            const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[prob] * a.w_stride : 0);
+            const uint8_t* xbase = a.xp + (size_t)prob * a.xp_stride;
             int early_kt0[STAGES], early_nkt[STAGES];
-            bool waited = false;
+            bool waited = multi;
             for (int it = begin; it < end; ++it) {
                 for (int sub = 0; sub < kItemTiles; sub += KTS) {
                     const int kt0 = st * kItemTiles + sub, nkt = min(KTS, KT - kt0);
@@ -217,13 +231,22 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     uint8_t* sb = stage0 + s * C::STAGE_BYTES;
                     const uint32_t wbytes = (uint32_t)(nkt * kWarps * C::REC), xbytes = (uint32_t)(nkt * C::XTILE);
                     mbar_arrive_expect_tx(full_bar(s), wbytes + xbytes);
-                    bulk_g2s(smem_u32(sb), a.w + ((size_t)cb * KT + kt0) * (kWarps * C::REC), wbytes, full_bar(s));
-                    if (waited) bulk_g2s(smem_u32(sb + C::W_BYTES), a.xp + (size_t)kt0 * C::XTILE, xbytes, full_bar(s));
+                    bulk_g2s(smem_u32(sb), wbase + ((size_t)cb * KT + kt0) * (kWarps * C::REC), wbytes, full_bar(s));
+                    if (waited) bulk_g2s(smem_u32(sb + C::W_BYTES), xbase + (size_t)kt0 * C::XTILE, xbytes, full_bar(s));
                     else { early_kt0[issued] = kt0; early_nkt[issued] = nkt; }
                     ++issued;
                     if (++s == STAGES) { s = 0; phase ^= 1; }
                 }
-                if (++st == SPB) { st = 0; ++cb; }
+                if (++st == SPB) {
+                    st = 0;
+                    ++gb;
+                    if (++cb == CB) {
+                        cb = 0;
+                        ++prob;
+                        if (multi && it + 1 < end) wbase = a.w + (size_t)a.prob_expert[prob] * a.w_stride;
+                        xbase = a.xp + (size_t)prob * a.xp_stride;
+                    }
+                }
             }
             if (!waited) {
                 pdl_wait();
@@ -240,7 +263,7 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
         // ------------------- finisher: sums parked segments while the consumers go on -----------
         if (part_first) {
             named_bar_sync(2, (kWarps + 1) * 32);
-            finish_segment<32>(a, cb_first, SPB, total, lane, seg_list[0]);
+            finish_segment<32>(a, cb_first, CB, SPB, total, lane, seg_list[0]);
         }
         return;
     }
@@ -253,8 +276,8 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     uint32_t phase = 0;
     int it = begin;
     while (it < end) {
-        const int cb = it / SPB;
-        const int cb_begin = cb * SPB, cb_end = cb_begin + SPB;
+        const int gb = it / SPB, prob = gb / CB, cb = gb - prob * CB;
+        const int cb_begin = gb * SPB, cb_end = cb_begin + SPB;
         const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
         for (int rb = 0; rb < MB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
@@ -323,8 +346,9 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                 for (int i = 0; i < 4; ++i) {
                     const int row = rb * 8 + 2 * t + (i & 1), col = col0 + (i >> 1) * 8;
                     if (row < a.M && col < a.N) {
-                        if (a.f32_out) reinterpret_cast<float*>(a.y)[(size_t)row * a.N + col] = acc[rb][i];
-                        else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)row * a.N + col] = f2bf(acc[rb][i]);
+                        const size_t at = (size_t)prob * a.y_stride + (size_t)row * a.N + col;
+                        if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = acc[rb][i];
+                        else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(acc[rb][i]);
                     }
                 }
         } else {
@@ -338,7 +362,7 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     const int row = rb * 8 + 2 * t + (i & 1);
                     if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
                 }
-            if (seg_end == end) finish_segment<kWarps * 32>(a, cb, SPB, total, threadIdx.x, seg_list[1]);
+            if (seg_end == end) finish_segment<kWarps * 32>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
             else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");   // the finisher takes it; go on
         }
     }
@@ -512,8 +536,40 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
     a.status = status;
     a.M = M; a.N = N; a.K = K;
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
+    a.prob_expert = nullptr; a.prob_count = nullptr; a.max_probs = 1;
+    a.w_stride = a.xp_stride = a.y_stride = 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return group == 64 ? tf::dispatch<64>(a, st) : tf::dispatch<32>(a, st);
+}
+
+int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count, int max_probs,
+                   void* y, void* scratch, size_t scratch_bytes, int N, int K, int group, int flags, int* status,
+                   void* stream) {
+    if (max_probs < 1 || N < 1 || K < 64 || K % 64) return TF_EINVAL;
+    if (group != 64 && group != 32) return TF_EINVAL;
+    if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
+    if (!x_packed || !w_tiled || !y || !prob_expert || !prob_count) return TF_EINVAL;
+    const long long CB = (N + tf::kCols - 1) / tf::kCols, SPB = (K / 64 + tf::kItemTiles - 1) / tf::kItemTiles;
+    if (CB * max_probs * 4 > TF_QMM_COUNTER_BYTES || CB * SPB * max_probs > (1 << 30) / tf::kWorkers) return TF_EINVAL;
+    if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
+    if ((uintptr_t)y & 3) return TF_EALIGN;
+    if (!scratch || ((uintptr_t)scratch & 255)) return TF_ESCRATCH;
+    if (scratch_bytes < tf_qmm_scratch_bytes()) return TF_ESCRATCH;
+    tf::Args a;
+    a.xp = static_cast<const uint8_t*>(x_packed);
+    a.w = static_cast<const uint8_t*>(w_tiled);
+    a.y = y;
+    a.counters = static_cast<int*>(scratch);
+    a.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + TF_QMM_COUNTER_BYTES);
+    a.status = status;
+    a.M = 8; a.N = N; a.K = K;
+    a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
+    a.prob_expert = prob_expert; a.prob_count = prob_count; a.max_probs = max_probs;
+    a.w_stride = (long long)tf_qmm_tiled_bytes(N, K, group);
+    a.xp_stride = (long long)tf_packed_bytes(8, K, group);
+    a.y_stride = 8ll * N;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return group == 64 ? tf::launch<64, 1, 4, tf::stages_for<64, 1, 4>()>(a, st) : tf::launch<32, 1, 4, tf::stages_for<32, 1, 4>()>(a, st);
 }
 
 int tf_qmm_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,
