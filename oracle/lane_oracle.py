@@ -342,6 +342,10 @@ class Config:
     rope_dims: int = 0
     rope_theta: float = 1e7
     group: int = 64
+    experts: int = 0                  # mixture-of-experts MLP when > 0 (``families/qwen4_exp/model.py``)
+    top_k: int = 0
+    moe_intermediate: int = 0
+    shared_expert: bool = True
 
     def __post_init__(self):
         if not self.rope_dims:
@@ -388,9 +392,16 @@ def random_model(cfg: Config, seed: int) -> dict:
     kd, vd = cfg.k_heads * cfg.dk, cfg.v_heads * cfg.dv
     layers = []
     for i in range(cfg.layers):
-        layer = {"linear": cfg.is_linear(i), "input_norm": norm(cfg.hidden), "post_norm": norm(cfg.hidden),
-                 "gate": random_q4(gen, cfg.intermediate, cfg.hidden, g), "up": random_q4(gen, cfg.intermediate, cfg.hidden, g),
-                 "down": random_q4(gen, cfg.hidden, cfg.intermediate, g)}
+        layer = {"linear": cfg.is_linear(i), "input_norm": norm(cfg.hidden), "post_norm": norm(cfg.hidden)}
+        if cfg.experts:
+            ne = cfg.experts + (1 if cfg.shared_expert else 0)
+            layer["router"] = (0.05 * torch.randn((ne, cfg.hidden), generator=gen)).to(BF16)
+            layer["experts"] = {"gate": [random_q4(gen, cfg.moe_intermediate, cfg.hidden, g) for _ in range(ne)],
+                                "up": [random_q4(gen, cfg.moe_intermediate, cfg.hidden, g) for _ in range(ne)],
+                                "down": [random_q4(gen, cfg.hidden, cfg.moe_intermediate, g) for _ in range(ne)]}
+        else:
+            layer.update(gate=random_q4(gen, cfg.intermediate, cfg.hidden, g), up=random_q4(gen, cfg.intermediate, cfg.hidden, g),
+                         down=random_q4(gen, cfg.hidden, cfg.intermediate, g))
         if layer["linear"]:
             layer.update(qkv=random_q4(gen, 2 * kd + vd, cfg.hidden, g), z=random_q4(gen, vd, cfg.hidden, g),
                          b=random_q4(gen, cfg.v_heads, cfg.hidden, g), a=random_q4(gen, cfg.v_heads, cfg.hidden, g),
@@ -476,6 +487,11 @@ def forward(model: dict, tokens: torch.Tensor, st: State, *, head: bool = True) 
             r = _lin(gate_mul(o, qg, heads=c.heads, head_dim=c.head_dim), layer["o"], g)
         x = (x.float() + r.float()).to(BF16)
         _, h = add_rmsnorm(x, None, layer["post_norm"], c.eps)
+        if "router" in layer:
+            e = layer["experts"]
+            pick, wts = moe_select(moe_router(h, layer["router"]), c.experts, c.top_k, c.shared_expert)
+            x = (x.float() + moe_experts(h, pick, wts, e["gate"], e["up"], e["down"], g).float()).to(BF16)
+            continue
         act = swiglu(_lin(h, layer["gate"], g), _lin(h, layer["up"], g))
         x = (x.float() + _lin(act, layer["down"], g).float()).to(BF16)
     st.pos += t

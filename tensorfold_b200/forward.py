@@ -19,6 +19,7 @@ import torch
 
 from . import lane_attention as LA
 from . import lane_gdn, lane_glue
+from . import lane_moe
 from .lane_qmm import MAX_ROWS, QWeight, lane_matmul, new_packed, tile_weight
 
 
@@ -43,6 +44,10 @@ class Config:
     rope_dims: int = 0
     rope_theta: float = 1e7
     group: int = 64
+    experts: int = 0                  # routed experts per layer; 0: dense SwiGLU MLP (``intermediate``)
+    top_k: int = 0
+    moe_intermediate: int = 0
+    shared_expert: bool = True        # one always-on expert, stored as expert id ``experts``
 
     def __post_init__(self):
         if not self.rope_dims:
@@ -77,6 +82,8 @@ class LayerWeights:
     norm: torch.Tensor | None = None
     q_norm: torch.Tensor | None = None
     k_norm: torch.Tensor | None = None
+    router: torch.Tensor | None = None       # MoE layers: [experts (+1), hidden] bf16; gate_up/down are then None
+    experts: object | None = None            # lane_moe.Experts
 
 
 @dataclass
@@ -93,7 +100,9 @@ class Weights:
 
         total = self.head.nbytes()
         for l in self.layers:
-            total += l.in_proj.nbytes() + l.out_proj.nbytes() + l.gate_up.nbytes() + l.down.nbytes()
+            total += l.in_proj.nbytes() + l.out_proj.nbytes()
+            if l.experts is None:
+                total += l.gate_up.nbytes() + l.down.nbytes()
         return total
 
 
@@ -120,15 +129,20 @@ def load_weights(model: dict, device="cuda") -> Weights:
     for src in model["layers"]:
         def dev(name):
             return src[name].to(device).contiguous()
+        moe = "router" in src
+        gate_up = None if moe else _stack([src["gate"], src["up"]], device, g)
+        down = None if moe else _stack([src["down"]], device, g)
+        extra = {}
+        if moe:
+            e = src["experts"]
+            extra = dict(router=dev("router"), experts=lane_moe.make_experts(e["gate"], e["up"], e["down"], g, device))
         if src["linear"]:
             lw = LayerWeights(True, dev("input_norm"), dev("post_norm"), _stack([src["qkv"], src["z"], src["b"], src["a"]], device, g),
-                              _stack([src["out"]], device, g), _stack([src["gate"], src["up"]], device, g),
-                              _stack([src["down"]], device, g), conv=dev("conv"), A_log=dev("A_log").float(),
-                              dt_bias=dev("dt_bias").float(), norm=dev("norm"))
+                              _stack([src["out"]], device, g), gate_up, down, conv=dev("conv"), A_log=dev("A_log").float(),
+                              dt_bias=dev("dt_bias").float(), norm=dev("norm"), **extra)
         else:
             lw = LayerWeights(False, dev("input_norm"), dev("post_norm"), _stack([src["q"], src["k"], src["v"]], device, g),
-                              _stack([src["o"]], device, g), _stack([src["gate"], src["up"]], device, g),
-                              _stack([src["down"]], device, g), q_norm=dev("q_norm"), k_norm=dev("k_norm"))
+                              _stack([src["o"]], device, g), gate_up, down, q_norm=dev("q_norm"), k_norm=dev("k_norm"), **extra)
         layers.append(lw)
     e = model["embed"]
     embed = (e.words.to(device).contiguous(), e.scales.to(device).contiguous(), e.biases.to(device).contiguous())
@@ -267,7 +281,12 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     q_att = torch.empty((R, c.heads, c.head_dim), **bf)
     o_att = torch.empty((R, c.heads, c.head_dim), **bf)
     att_in = torch.empty((R, c.heads * 2 * c.head_dim + 2 * c.kv_heads * c.head_dim), **bf)
-    mlp_in = torch.empty((R, 2 * c.intermediate), **bf)
+    mlp_in = torch.empty((R, 2 * c.intermediate), **bf) if c.experts == 0 else None
+    moe_buf = None
+    if c.experts:
+        if tp is not None:
+            raise ValueError("tree_forward: mixture-of-experts layers shard by expert, not by tensor-parallel rank")
+        moe_buf = lane_moe.MoEBuffers(R, c.experts, c.top_k, c.shared_expert, c.hidden, c.moe_intermediate, g, dev)
     scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
     scale = c.head_dim ** -0.5
 
@@ -305,6 +324,10 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
             mixed = lane_glue.gate_mul(o_att, proj[:, :nq], heads=c.heads, head_dim=c.head_dim, group=g)
             ai += 1
         r, rparts = row_parallel(mixed, layer.out_proj)
+        if layer.experts is not None:
+            x, hrows = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts, rows_out=True, packed_out=False)
+            pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf), None
+            continue
         x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts)
         gu = lane_matmul(h, layer.gate_up, out=mlp_in)
         act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)

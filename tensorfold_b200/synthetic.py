@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from .forward import Config, LayerWeights, Weights
+from .lane_moe import Experts
 from .lane_qmm import QWeight, tile_weight
 
 
@@ -44,19 +45,28 @@ def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, wor
     for i in range(cfg.layers):
         linear = cfg.is_linear(i)
         inorm, pnorm = norm(cfg.hidden), norm(cfg.hidden)
-        gate_up = random_q4(gen, 2 * sc.intermediate, cfg.hidden, g, device)
-        down = random_q4(gen, cfg.hidden, sc.intermediate, g, device)
+        extra = {}
+        if cfg.experts:
+            ne = cfg.experts + (1 if cfg.shared_expert else 0)
+            gate_up = down = None
+            gu = [random_q4(gen, 2 * cfg.moe_intermediate, cfg.hidden, g, device).tiled for _ in range(ne)]
+            dn = [random_q4(gen, cfg.hidden, cfg.moe_intermediate, g, device).tiled for _ in range(ne)]
+            extra = dict(router=(0.05 * torch.randn((ne, cfg.hidden), generator=gen, device=device)).to(bf),
+                         experts=Experts(torch.cat(gu), torch.cat(dn), ne, cfg.hidden, cfg.moe_intermediate, g))
+        else:
+            gate_up = random_q4(gen, 2 * sc.intermediate, cfg.hidden, g, device)
+            down = random_q4(gen, cfg.hidden, sc.intermediate, g, device)
         if linear:
             lw = LayerWeights(True, inorm, pnorm, random_q4(gen, 2 * kd + 2 * vd + 2 * sc.v_heads, cfg.hidden, g, device),
                               random_q4(gen, cfg.hidden, vd, g, device), gate_up, down,
                               conv=(0.3 * torch.randn((2 * kd + vd, 4), generator=gen, device=device)).to(bf),
                               A_log=0.5 * torch.randn(sc.v_heads, generator=gen, device=device),
-                              dt_bias=0.5 * torch.randn(sc.v_heads, generator=gen, device=device), norm=norm(128))
+                              dt_bias=0.5 * torch.randn(sc.v_heads, generator=gen, device=device), norm=norm(128), **extra)
         else:
             nq = sc.heads * 2 * cfg.head_dim + 2 * sc.kv_heads * cfg.head_dim
             lw = LayerWeights(False, inorm, pnorm, random_q4(gen, nq, cfg.hidden, g, device),
                               random_q4(gen, cfg.hidden, sc.heads * cfg.head_dim, g, device), gate_up, down,
-                              q_norm=norm(cfg.head_dim), k_norm=norm(cfg.head_dim))
+                              q_norm=norm(cfg.head_dim), k_norm=norm(cfg.head_dim), **extra)
         layers.append(lw)
     words = torch.randint(-2 ** 31, 2 ** 31 - 1, (cfg.vocab, cfg.hidden // 8), generator=rgen, dtype=torch.int64, device=device).to(torch.int32)
     s = ((torch.rand((cfg.vocab, cfg.hidden // g), generator=rgen, device=device) / 8 + 1 / 64) * 0.5).to(bf)
@@ -65,8 +75,12 @@ def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, wor
     return Weights(sc, embed, layers, norm(cfg.hidden), head, cfg.inv_freq().to(device))
 
 
+MOE_30B = dict(hidden=2048, intermediate=0, layers=48, heads=16, kv_heads=2, head_dim=256, vocab=151936, k_heads=16, v_heads=32,
+               dk=128, dv=128, conv_kernel=4, interval=4, eps=1e-6, rope_dims=64, rope_theta=1e7, group=32, experts=128, top_k=8,
+               moe_intermediate=768, shared_expert=True)
+
 DENSE_27B = dict(hidden=5120, intermediate=17408, layers=64, heads=24, kv_heads=4, head_dim=256, vocab=248320, k_heads=16,
                  v_heads=32, dk=128, dv=128, conv_kernel=4, interval=4, eps=1e-6, rope_dims=64, rope_theta=1e7, group=64)
 
 
-__all__ = ["DENSE_27B", "random_q4", "random_weights"]
+__all__ = ["DENSE_27B", "MOE_30B", "random_q4", "random_weights"]
