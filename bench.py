@@ -201,6 +201,7 @@ def main():
     ap.add_argument("--synthetic-context", action="store_true",
                     help="skip the prefill: set the context length directly (KV pages and recurrent state stay zero); for profiler runs")
     ap.add_argument("--no-spinup", action="store_true", help="skip the half second of untimed steps that brings the clocks up")
+    ap.add_argument("--exchange", default="peer", help="tensor-parallel exchange: 'peer' (own kernel over NVLink peer memory) or 'nccl'")
     ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit")
     ap.add_argument("--shape", default="17408x5120")
     ap.add_argument("--rows", type=int, default=8)
@@ -211,7 +212,7 @@ def main():
     rows = args.seqs * args.width
     workload = (f"dense hybrid 27B-class 4-bit g64 verify forward: {args.layers} layers (3 gated-DeltaNet : 1 GQA), hidden 5120, "
                 f"MLP 17408, vocab 248320; {args.seqs} sequences x W={args.width} rows, context {args.ctx}")
-    config = {"workload": workload, "seqs": args.seqs, "width": args.width, "context": args.ctx, "parallelism": f"tp{world}",
+    config = {"workload": workload, "seqs": args.seqs, "width": args.width, "context": args.ctx, "parallelism": f"tp{world}" + (f" ({args.exchange} exchange)" if world > 1 else ""),
               "l2": "weights (13.6 GB per forward) exceed the 126 MB L2; no flush needed"}
 
     if args.impl == "reference":
@@ -242,7 +243,7 @@ def main():
         from tensorfold_b200 import distributed
 
         dist.init_process_group("nccl", device_id=dev)
-        tp = distributed.RankGroup()
+        tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
 

@@ -280,6 +280,20 @@ int tf_moe_pack(const void* x, size_t x_stride, const int* prob_rows, const int*
 int tf_moe_act(const void* gate_up, const int* prob_count, int max_probs, void* act_packed, int I, int group, void* stream);
 int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* stream);
 
+/* ---- tensor-parallel exchange over peer memory ---------------------------------------------------
+ * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (gather_rank_partials over NCCL) and the
+ * hand-bound collective of families/qwen4_exp/cuda/comm.py:41-85.
+ * One call per rank and exchange: the rank's fp32 partial local [rows, D] is stored into block `rank`
+ * of the slot at slot_off of EVERY rank's buffer (peer_bufs: device array of the world's buffer base
+ * addresses, the same symmetric allocation on every rank), then the ranks signal and wait for one
+ * another through the flag words at flags_off (4 bytes per rank, zero before the first exchange).
+ * When the call's kernel has finished, the local buffer holds [world, rows, D] at slot_off. seq and
+ * tickets: one zero-initialised 32-bit word each in local device memory, private to this rank group.
+ * Consecutive exchanges must alternate between two slots; all ranks must issue the same exchanges in
+ * the same order. The wait is bounded and reports TF_ESTALL through `status`. */
+int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t flags_off, size_t slot_off, int rank,
+                     int world, void* seq, void* tickets, int* status, void* stream);
+
 /* ---- exact top-k and keyed sampling --------------------------------------------------------------
  * Each row's k largest bf16 logits (k <= 64), ordered by value descending then id ascending; ties at
  * the cut go to the smallest ids. idx int32 [rows, k], val fp32 [rows, k]. scratch: the slices'

@@ -75,6 +75,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_moe_pack": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_act": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "tf_peer_exchange": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                 c_void_p]),
     "tf_topk_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tf_sample_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_ulonglong, c_double, c_int, c_double, c_void_p,

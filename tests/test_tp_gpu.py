@@ -15,13 +15,13 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_window_rows_equal_serial_steps_under_tp(lib, world):
+@pytest.mark.parametrize("world,exchange", [(2, "peer"), (2, "nccl"), (4, "peer"), (8, "peer")])
+def test_window_rows_equal_serial_steps_under_tp(lib, world, exchange):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", TP_EXCHANGE=exchange)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29400 + world), str(ROOT / "tests" / "tp_worker.py")]
+           "--master-port", str(29400 + world + (20 if exchange == "nccl" else 0)), str(ROOT / "tests" / "tp_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     m = re.search(r"TP_RESULT world=(\d+) window_equals_serial=(\d) head_ok=(\d) cos_vs_one_gpu=([0-9.]+)", out.stdout)

@@ -30,8 +30,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    tp = distributed.RankGroup()
     cfg = O.Config(**SMALL)
+    tp = distributed.RankGroup(exchange=os.environ.get("TP_EXCHANGE", "peer"), hidden=cfg.hidden, device=dev)
     model = O.random_model(cfg, seed=5)                       # the same full model on every rank
     w = F.load_weights(distributed.split_model(model, rank, world), dev)
     gen = torch.Generator().manual_seed(3)
@@ -79,6 +79,8 @@ def main():
     flags = torch.tensor([int(same), int(head_ok)], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
+        from tensorfold_b200 import _lib
+        _lib.status(dev).raise_if_set()
         print(f"TP_RESULT world={world} window_equals_serial={int(flags[0])} head_ok={int(flags[1])} cos_vs_one_gpu={cos:.6f}", flush=True)
     dist.destroy_process_group()
 
