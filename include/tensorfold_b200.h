@@ -283,15 +283,17 @@ int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int sl
 /* ---- tensor-parallel exchange over peer memory ---------------------------------------------------
  * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (gather_rank_partials over NCCL) and the
  * hand-bound collective of families/qwen4_exp/cuda/comm.py:41-85.
- * One call per rank and exchange: the rank's fp32 partial local [rows, D] is stored into block `rank`
- * of the slot at slot_off of EVERY rank's buffer (peer_bufs: device array of the world's buffer base
- * addresses, the same symmetric allocation on every rank), then the ranks signal and wait for one
- * another through the flag words at flags_off (4 bytes per rank, zero before the first exchange).
- * When the call's kernel has finished, the local buffer holds [world, rows, D] at slot_off. seq and
- * tickets: one zero-initialised 32-bit word each in local device memory, private to this rank group.
- * Consecutive exchanges must alternate between two slots; all ranks must issue the same exchanges in
- * the same order. The wait is bounded and reports TF_ESTALL through `status`. */
-int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t flags_off, size_t slot_off, int rank,
+ * One call per rank and exchange: the rank's fp32 partial local [rows, D] is turned into 16-byte
+ * packets {value, n, value, n} (n = the exchange number, a device counter every rank advances alike)
+ * and stored into block `rank` of the slot at slot_off of EVERY rank's buffer (peer_bufs: device array
+ * of the world's buffer base addresses, the same symmetric allocation on every rank, zero before the
+ * first exchange); each rank then polls its own slot until every packet carries n and writes the
+ * payload to `gathered` [world, rows, D] fp32 (local memory). A slot is tf_peer_slot_bytes bytes.
+ * seq and tickets: one zero-initialised 32-bit word each in local device memory, private to this rank
+ * group. Consecutive exchanges must alternate between two slots; all ranks must issue the same
+ * exchanges in the same order. The polling is bounded and reports TF_ESTALL through `status`. */
+size_t tf_peer_slot_bytes(int rows, int D, int world);
+int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_off, float* gathered, int rank,
                      int world, void* seq, void* tickets, int* status, void* stream);
 
 /* ---- exact top-k and keyed sampling --------------------------------------------------------------

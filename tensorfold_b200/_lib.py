@@ -75,7 +75,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_moe_pack": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_act": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
-    "tf_peer_exchange": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p,
+    "tf_peer_slot_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tf_peer_exchange": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_void_p]),
     "tf_topk_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -86,7 +87,7 @@ SIGNATURES: dict[str, tuple] = {
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
 _NO_LAUNCH = {"tf_version", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems"}
+              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_peer_slot_bytes"}
 
 
 def launch_count() -> int:

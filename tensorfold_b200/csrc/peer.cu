@@ -1,18 +1,21 @@
 // Tensor-parallel exchange over peer memory (NVLink / NVSwitch): every rank ends up with all ranks'
-// fp32 partials of a row-parallel projection, stacked in rank order, without a library collective.
+// fp32 partials of a row-parallel projection, stacked in rank order, without a library collective
+// and without a fence or a round trip on the critical path.
 //
-// Each rank owns a buffer in symmetric memory: [flags: one 32-bit word per rank][two slots of
-// world x rows x D fp32]. One exchange = one kernel per rank:
-//   push    every CTA copies a share of the local partial into slot s, block `rank`, of EVERY rank's
-//           buffer (plain 16-byte peer stores; its own buffer included), then fences at system scope
-//           and takes a ticket;
-//   signal  the last CTA writes the exchange number into flags[rank] of every rank (release, system);
-//   wait    and spins (acquire, system; bounded) until its own flags show that number from every
-//           rank, so the kernel that follows in the stream may read the gathered partials.
-// The exchange number is a device counter that every rank advances identically; slots alternate
-// (chosen by the host, fixed per launch) so that a fast rank's next push never lands in a block a
-// slower rank is still reading: pushing exchange n+2 into the slot of exchange n requires having
-// passed the wait of n+1, which every rank signals only after it consumed n.
+// Each rank owns a buffer in symmetric memory with two "packet" slots. A packet is 16 bytes:
+// {value, n, value, n} - two fp32 payload words, each followed by the exchange number n. One exchange =
+// one kernel per rank:
+//   push    every thread turns its share of the local partial into packets and stores them into
+//           block `rank` of the slot in EVERY rank's buffer (plain 16-byte peer stores, own buffer
+//           included). The payload carries its own arrival signal, so nothing else is sent.
+//   gather  every thread then polls its share of the local slot, block by block in rank order, until
+//           both exchange numbers of a packet read n (bounded spin), and writes the payload to the
+//           plain [world, rows, D] fp32 array the next kernel reads.
+// The exchange number is a device counter every rank advances identically; 8-byte halves of a packet
+// are written atomically, and a stale packet carries an older number, so a reader never mixes
+// exchanges. Slots alternate (chosen by the host, fixed per launch): a rank can only push exchange
+// n+2 into the slot of n after passing the gather of n+1, which needs every rank's push of n+1, which
+// each rank issues only after it has consumed n.
 // The sum itself (rank order, one rounding) is fused into the kernel that consumes the partials.
 //
 // No multicast of any kind is used: plain stores to peer addresses only.
@@ -22,46 +25,50 @@
 namespace tf {
 namespace {
 
-constexpr unsigned kSpinLimit = 1u << 25;     // x ~100 ns: a few seconds, then TF_ESTALL is reported
+constexpr unsigned kSpinLimit = 1u << 24;     // polls of one packet (each a memory round trip): seconds, then TF_ESTALL
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_volatile16(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
-__global__ void __launch_bounds__(256) peer_exchange_kernel(const float4* local, int n4, uint8_t* const* bufs, size_t dst_off,
-                                                            size_t flags_off, int rank, int world, uint32_t* seq, int* tickets,
+// n2 = rows * D / 2 packets per rank block
+__global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local, int n2, uint8_t* const* bufs, size_t slot_off,
+                                                            float2* gathered, int rank, int world, uint32_t* seq, int* tickets,
                                                             int* status) {
     __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t want = *reinterpret_cast<volatile uint32_t*>(seq) + 1u;
-    const int stride = gridDim.x * blockDim.x;
-    for (int peer = 0; peer < world; ++peer) {
-        float4* dst = reinterpret_cast<float4*>(bufs[peer] + dst_off);
-        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) dst[i] = local[i];
+    const int stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+    for (int i = first; i < n2; i += stride) {
+        const float2 v = local[i];
+        const uint4 pkt = make_uint4(__float_as_uint(v.x), want, __float_as_uint(v.y), want);
+        for (int peer = 0; peer < world; ++peer)
+            st_volatile16(reinterpret_cast<uint4*>(bufs[peer] + slot_off) + (size_t)rank * n2 + i, pkt);
     }
-    __threadfence_system();
+    const uint4* mine = reinterpret_cast<const uint4*>(bufs[rank] + slot_off);
+    bool stalled = false;
+    for (int r = 0; r < world; ++r) {
+        for (int i = first; i < n2; i += stride) {
+            uint4 pkt = ld_volatile16(mine + (size_t)r * n2 + i);
+            unsigned spins = 0;
+            while ((pkt.y != want || pkt.w != want) && !stalled) {
+                if (++spins > kSpinLimit) { stalled = true; break; }
+                pkt = ld_volatile16(mine + (size_t)r * n2 + i);
+            }
+            gathered[(size_t)r * n2 + i] = make_float2(__uint_as_float(pkt.x), __uint_as_float(pkt.z));
+        }
+    }
+    if (stalled) report(status, TF_ESTALL);
     __syncthreads();
     if (threadIdx.x == 0) is_last = atomicAdd(tickets, 1) == (int)gridDim.x - 1;
     __syncthreads();
-    if (!is_last) return;
-    __threadfence_system();
-    if (threadIdx.x < world) {
-        st_release_sys(reinterpret_cast<uint32_t*>(bufs[threadIdx.x] + flags_off) + rank, want);
-        const uint32_t* mine = reinterpret_cast<const uint32_t*>(bufs[rank] + flags_off) + threadIdx.x;
-        unsigned spins = 0;
-        while ((int)(ld_acquire_sys(mine) - want) < 0) {
-            if (++spins > kSpinLimit) { report(status, TF_ESTALL); break; }
-            __nanosleep(64);
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    if (is_last && threadIdx.x == 0) {
         *tickets = 0;
         *reinterpret_cast<volatile uint32_t*>(seq) = want;
     }
@@ -72,20 +79,25 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const float4* local,
 
 extern "C" {
 
-int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t flags_off, size_t slot_off, int rank,
+size_t tf_peer_slot_bytes(int rows, int D, int world) {
+    if (rows < 1 || D < 2 || world < 1) return 0;
+    return (size_t)world * rows * D * 8;            // a 16-byte packet per two fp32 values
+}
+
+int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_off, float* gathered, int rank,
                      int world, void* seq, void* tickets, int* status, void* stream) {
     if (rows < 1 || D < 4 || D % 4 || world < 2 || world > 64 || rank < 0 || rank >= world) return TF_EINVAL;
-    if (!local || !peer_bufs || !seq || !tickets) return TF_EINVAL;
-    if (((uintptr_t)local | slot_off | flags_off) & 15) return TF_EALIGN;
-    const float4* src = reinterpret_cast<const float4*>(local);
-    int n4 = rows * (D / 4);
-    size_t dst_off = slot_off + (size_t)rank * rows * D * sizeof(float);
+    if (!local || !peer_bufs || !gathered || !seq || !tickets) return TF_EINVAL;
+    if (((uintptr_t)local | (uintptr_t)gathered | slot_off) & 15) return TF_EALIGN;
+    const float2* src = reinterpret_cast<const float2*>(local);
+    float2* dst = reinterpret_cast<float2*>(gathered);
+    int n2 = rows * (D / 2);
     uint32_t* seq_p = static_cast<uint32_t*>(seq);
     int* tick_p = static_cast<int*>(tickets);
     uint8_t* const* bufs = reinterpret_cast<uint8_t* const*>(peer_bufs);
-    int blocks = (n4 + 255) / 256;
-    if (blocks > 32) blocks = 32;
-    void* args[] = {&src, &n4, &bufs, &dst_off, &flags_off, &rank, &world, &seq_p, &tick_p, &status};
+    int blocks = (n2 + 255) / 256;
+    if (blocks > 64) blocks = 64;      // few enough to be resident together beside the neighbouring kernels
+    void* args[] = {&src, &n2, &bufs, &slot_off, &dst, &rank, &world, &seq_p, &tick_p, &status};
     return tf::launch_pdl((const void*)tf::peer_exchange_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
                           args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }

@@ -59,8 +59,6 @@ class RankGroup:
     kernel. ``exchange="nccl"``: ``all_gather_into_tensor`` on the current stream (gloo on CPU in
     tests). Never an all-reduce: the sum is done in rank order by the consuming kernel."""
 
-    FLAG_BYTES = 256
-
     def __init__(self, group=None, exchange: str = "nccl", max_rows: int = 128, hidden: int = 0, device=None):
         import torch.distributed as dist
 
@@ -78,9 +76,10 @@ class RankGroup:
 
             if hidden <= 0 or device is None:
                 raise ValueError("peer exchange needs the hidden size and the device")
-            self.slot_bytes = self.world * max_rows * hidden * 4
-            total = self.FLAG_BYTES + 2 * self.slot_bytes
-            self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+            from . import _lib
+
+            self.slot_bytes = _lib.load().tf_peer_slot_bytes(max_rows, hidden, self.world)
+            self.buf = symm_mem.empty(2 * self.slot_bytes, dtype=torch.uint8, device=device)
             self.buf.zero_()
             self.handle = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
             self.state = torch.zeros(2, dtype=torch.int32, device=device)       # exchange number, CTA tickets
@@ -98,16 +97,19 @@ class RankGroup:
             from . import _lib
 
             m, d = local.shape
-            if self.world * m * d * 4 > self.slot_bytes:
+            lib = _lib.load()
+            if lib.tf_peer_slot_bytes(m, d, self.world) > self.slot_bytes:
                 raise ValueError("partial larger than the exchange buffer")
-            slot_off = self.FLAG_BYTES + (self.count & 1) * self.slot_bytes
+            slot_off = (self.count & 1) * self.slot_bytes
             self.count += 1
             local = local.contiguous()
+            if out is None:
+                out = torch.empty((self.world, m, d), dtype=torch.float32, device=local.device)
             with torch.cuda.device(local.device):
-                _lib.check(_lib.load().tf_peer_exchange(local.data_ptr(), m, d, self.handle.buffer_ptrs_dev, 0, slot_off, self.rank,
-                                                        self.world, self.state[0:1].data_ptr(), self.state[1:2].data_ptr(),
-                                                        _lib.status(local.device).word.data_ptr(), _lib.stream()), "peer exchange")
-            return self.buf[slot_off:slot_off + self.world * m * d * 4].view(torch.float32).view(self.world, m, d)
+                _lib.check(lib.tf_peer_exchange(local.data_ptr(), m, d, self.handle.buffer_ptrs_dev, slot_off, out.data_ptr(), self.rank,
+                                                self.world, self.state[0:1].data_ptr(), self.state[1:2].data_ptr(),
+                                                _lib.status(local.device).word.data_ptr(), _lib.stream()), "peer exchange")
+            return out
         if out is None:
             out = torch.empty((self.world, *local.shape), dtype=torch.float32, device=local.device)
         # the collective wants the ranks' blocks concatenated along dim 0
