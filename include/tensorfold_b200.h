@@ -212,7 +212,7 @@ int tf_conv_commit(const void* qkv, size_t qkv_stride, long long rec_qkv_stride,
  * Causal GQA for every window row of every sequence: row t of sequence s attends to the committed
  * tokens 0..seq_lens[s]-1 (pages: k_pages / v_pages [page, kv_head, 16, D] bf16 through
  * page_table [n_seqs, max_pages]) and to window rows 0..t of s (k_new / v_new [rows, kv_heads, D]).
- * Keys are cut by absolute position into 512-key chunks of 64-key tiles; per-chunk (m, l, O)
+ * Keys are cut by absolute position into 256-key chunks of 64-key tiles; per-chunk (m, l, O)
  * partials go to `scratch` (tf_attention_scratch_bytes) and are merged in chunk order.
  * row_nkeys[row] = seq_lens[s] + t + 1. max_window = longest window, max_chunks >= ceil(max over s of
  * (seq_lens[s] + window) / 512). q, out [rows, heads, D]; D = 128 or 256; heads/kv_heads <= 16.

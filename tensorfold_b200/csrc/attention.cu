@@ -2,7 +2,7 @@
 //
 // Keys of a sequence are its committed tokens (positions 0..L-1, read through the page table) followed
 // by the window's own rows (positions L.., read from the forward's uncommitted K/V rows); window row t
-// sees positions 0..L+t. The key axis is cut by ABSOLUTE position into 512-key chunks of eight 64-key
+// sees positions 0..L+t. The key axis is cut by ABSOLUTE position into 256-key chunks of four 64-key
 // tiles; one CTA handles (sequence, KV head, chunk) for all window rows and all query heads of that
 // KV head at once (rows of 16 = one tensor-core tile a warp), with an fp32 online softmax per query
 // row over the tiles in order, and writes per-chunk partials (m, l, O). A second kernel merges the
@@ -21,7 +21,7 @@
 namespace tf {
 namespace {
 
-constexpr int kChunk = 512, kTileKeys = 64, kPage = 16, kQRows = 64, kAttnWarps = 4;
+constexpr int kChunk = 256, kTileKeys = 64, kPage = 16, kQRows = 64, kAttnWarps = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnArgs {

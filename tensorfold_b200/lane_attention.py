@@ -13,7 +13,7 @@ import torch
 from . import _lib
 
 PAGE = 16
-CHUNK = 512
+CHUNK = 256
 
 
 class PagedKV:
@@ -68,7 +68,7 @@ def lane_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_
 
     k_new, v_new (R, HK, D) window rows; k_pages, v_pages (pages, HK, 16, D); page_table (S, max_pages),
     seq_lens (S,), seq_start (S+1,), row_nkeys (R,) int32 on the device (row_nkeys = committed length +
-    place in window + 1). ``max_window`` bounds a sequence's rows, ``max_chunks`` the 512-key chunks.
+    place in window + 1). ``max_window`` bounds a sequence's rows, ``max_chunks`` the 256-key chunks.
     """
 
     _lib.need_cuda(q, k_new, v_new, k_pages, v_pages, page_table, seq_lens, seq_start, row_nkeys)

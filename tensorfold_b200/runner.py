@@ -28,7 +28,7 @@ class LaneRunner:
                 st.kv.reserve(s, max_context + wd)     # pages for the whole run: the captured graph never reallocates
         st.kv.sync_table()
         st.sync_lens()
-        chunks = -(-(max_context + max(widths)) // 512)
+        chunks = -(-(max_context + max(widths)) // 256)
         self.batch: Batch = make_batch(st, widths, dev, max_chunks=chunks)
         self.rows = self.batch.rows
         self.tokens = torch.zeros(self.rows, dtype=torch.int32, device=dev)

@@ -150,7 +150,8 @@ def test_lane_attention_ragged_windows(lib, d, h, hk):
     lens, widths = [0, 5, 509, 1030, 3], [3, 8, 8, 1, 16]
     kv, q, k_new, v_new, keys, vals, starts, nkeys = paged_setup(3, lens, widths, h, hk, d)
     seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
-    args = dict(scale=d ** -0.5, max_window=max(widths), max_chunks=3)
+    need = -(-(max(lens) + max(widths)) // LA.CHUNK)
+    args = dict(scale=d ** -0.5, max_window=max(widths), max_chunks=need)
     out = LA.lane_attention(q.cuda(), k_new.cuda(), v_new.cuda(), kv.k[0], kv.v[0], kv.table, seq_lens, starts.cuda(),
                             nkeys.cuda(), **args)
     r0 = 0
@@ -169,11 +170,11 @@ def test_lane_attention_ragged_windows(lib, d, h, hk):
             kv2.v[0, page, :, p % 16] = vals[i][p].cuda()
         one = LA.lane_attention(q[r:r + 1].cuda(), k_new[r:r + 1].cuda(), v_new[r:r + 1].cuda(), kv2.k[0], kv2.v[0], kv2.table,
                                 torch.tensor([lens[i] + t], dtype=torch.int32).cuda(), torch.tensor([0, 1], dtype=torch.int32).cuda(),
-                                nkeys[r:r + 1].cuda(), scale=d ** -0.5, max_window=1, max_chunks=3)
+                                nkeys[r:r + 1].cuda(), scale=d ** -0.5, max_window=1, max_chunks=need)
         assert_same_bits(one, out[r:r + 1], f"seq {i} row {t}: window row == serial row")
     # a larger chunk budget than needed changes nothing
     out2 = LA.lane_attention(q.cuda(), k_new.cuda(), v_new.cuda(), kv.k[0], kv.v[0], kv.table, seq_lens, starts.cuda(),
-                             nkeys.cuda(), scale=d ** -0.5, max_window=max(widths), max_chunks=7)
+                             nkeys.cuda(), scale=d ** -0.5, max_window=max(widths), max_chunks=need + 4)
     assert_same_bits(out2, out, "chunk budget")
 
 
