@@ -137,3 +137,21 @@ def test_split_model_shards_reassemble_into_the_stored_model():
             assert torch.equal(s["layers"][3]["k"].words, att["k"].words[h0 * 128:(h0 + per) * 128])
             assert s["config"].kv_heads == per and s["config"].vocab == cfg.vocab // world
         assert torch.equal(torch.cat([s["head"].words for s in shards]), model["head"].words)
+
+
+def test_copy_drafter_and_digest():
+    """Host logic of the round loop (reference: decode.CopyIndex, copy_chain)."""
+
+    from tensorfold_b200.decode import CopyIndex, DecodeResult
+    from tensorfold_b200.forward import accept_path
+
+    ctx = [1, 2, 3, 4, 9, 9, 1, 2, 3]
+    idx = CopyIndex(min_match=2)
+    assert idx.propose(ctx, 3) == [4, 9, 9]              # continuation after the earlier "2 3"
+    ctx += [4, 9]
+    assert idx.propose(ctx, 2) == [9, 1]                 # the index follows the growing context
+    assert CopyIndex().propose([5, 6, 7], 4) == []       # nothing seen twice
+    assert accept_path([10, 11, 12, 13], [11, 12, 99, 7]) == 3
+    assert accept_path([10, 11], [5, 5]) == 1
+    a, b = DecodeResult([[1, 2], [3]], 0.0, 1), DecodeResult([[1, 2], [3]], 1.0, 2)
+    assert a.sha256() == b.sha256() != DecodeResult([[1, 2, 3]], 0.0, 1).sha256()
