@@ -145,22 +145,36 @@ def only_qmm(args, dev):
 
     import torch
 
-    from tensorfold_b200 import _lib, lane_qmm, synthetic
+    from tensorfold_b200 import _lib, lane_qmm, prefill_qmm, synthetic
 
     n, k = (int(v) for v in args.shape.split("x"))
     group, rows = 64, args.rows
     gen = torch.Generator(device=dev).manual_seed(3)
-    ws = [synthetic.random_q4(gen, n, k, group, dev) for _ in range(args.copies)]
-    x = lane_qmm.pack_rows(torch.randn((rows, k), device=dev, generator=gen).to(torch.bfloat16), group)
-    out = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    xr = torch.randn((rows, k), device=dev, generator=gen).to(torch.bfloat16)
+    if args.only == "prefill":
+        def weight():
+            words = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, dtype=torch.int64, device=dev).to(torch.int32)
+            sc = ((torch.rand((n, k // group), generator=gen, device=dev) / 8 + 1 / 64) * (4.0 / k ** 0.5)).to(torch.bfloat16)
+            return prefill_qmm.tile_weight(words, sc, (-7.5 * sc.float()).to(torch.bfloat16), group)
+        ws = [weight() for _ in range(args.copies)]
+
+        def run(q):
+            return prefill_qmm.prefill_matmul(xr, q)        # packs the rows, then the tcgen05 matmul
+    else:
+        ws = [synthetic.random_q4(gen, n, k, group, dev) for _ in range(args.copies)]
+        x = lane_qmm.pack_rows(xr, group)
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+
+        def run(q):
+            return lane_qmm.lane_matmul(x, q, out=out)
     for q in ws:
-        lane_qmm.lane_matmul(x, q, out=out)
+        run(q)
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = max(args.steps, 1) * args.copies
     e0.record()
     for i in range(launches):
-        lane_qmm.lane_matmul(x, ws[i % args.copies], out=out)
+        run(ws[i % args.copies])
     e1.record()
     torch.cuda.synchronize(dev)
     _lib.status(dev).raise_if_set()
@@ -168,9 +182,82 @@ def only_qmm(args, dev):
     kg = k // group
     alg = n * k // 2 + n * kg * 4 + rows * k * 2 + rows * kg * 4 + rows * n * 2
     peak, kind = peaks()
-    print(json.dumps({"only": "qmm", "shape": [n, k], "rows": rows, "launches": launches, "us_per_launch": us,
+    flops = 2.0 * rows * n * k
+    print(json.dumps({"only": args.only, "tflops": flops / us / 1e6, "shape": [n, k], "rows": rows, "launches": launches, "us_per_launch": us,
                       "note": "eager launches back to back (includes launch gaps); the graph-replayed figure is in the main line",
                       "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
+
+
+def bench_moe(args, dev):
+    """BASELINE config 4 on one GPU: 48-layer MoE hybrid, 32 sequences with draft widths uniform in 1..8
+    (redrawn until they fit the 128-row forward) and contexts uniform in 1k..16k. The context is set
+    synthetically (zero KV pages and recurrent state: same kernels, same traffic)."""
+
+    import random
+
+    import torch
+
+    from tensorfold_b200 import _lib, forward as F, runner, synthetic
+
+    cfg = F.Config(**dict(synthetic.MOE_30B, layers=min(args.layers, 48)))
+    w = synthetic.random_weights(cfg, seed=2, device=dev)
+    rng = random.Random(11)
+    seqs = 32
+    widths = [rng.randint(1, 8) for _ in range(seqs)]
+    while sum(widths) > 128:
+        widths = [rng.randint(1, 8) for _ in range(seqs)]
+    ctxs = [rng.randint(1024, 16384) for _ in range(seqs)]
+    rows = sum(widths)
+    st = F.State(w, seqs, max(ctxs) + 16, dev)
+    run = runner.LaneRunner(w, st, widths, max_context=max(ctxs) + 8)
+    run.capture()
+    st.lens = list(ctxs)
+    run.refresh()
+    gen = torch.Generator(device=dev).manual_seed(7)
+    run.tokens.copy_(torch.randint(0, cfg.vocab, (rows,), generator=gen, device=dev, dtype=torch.int32))
+    for _ in range(max(args.warmup, 3)):
+        run.step_device()
+    t_end = time.time() + (0.0 if args.no_spinup else 0.5)
+    while time.time() < t_end:
+        run.step_device()
+        torch.cuda.synchronize(dev)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index or 0) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            run.step_device()
+        e1.record()
+        torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1)
+    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run.step(host_tokens)
+    torch.cuda.synchronize(dev)
+    e2e_s = time.perf_counter() - t0
+    _lib.status(dev).raise_if_set()
+    peak, kind = peaks()
+    g = cfg.group
+    bits = 0.5 + 4.0 / g
+    dense = w.nbytes()
+    per_expert = (3 * cfg.moe_intermediate * cfg.hidden) * bits
+    touched = min(cfg.experts, rows * cfg.top_k) + 1          # upper bound of distinct experts a layer streams
+    print(json.dumps({
+        "metric": "lane-verify rows/sec", "value": args.steps * rows / (ms / 1000.0), "unit": "rows/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"MoE hybrid 30B-A3B-class 4-bit g32 verify forward: {cfg.layers} layers, hidden 2048, 128 experts top-8 + "
+                               f"shared, expert width 768; 32 sequences, draft widths uniform 1..8 ({rows} rows), contexts uniform 1k..16k "
+                               "(set synthetically)", "seqs": seqs, "rows": rows, "parallelism": "single GPU",
+                   "l2": "weights streamed per forward exceed the 126 MB L2; no flush needed"},
+        "clocks": clk.summary(),
+        "e2e": {"value": args.steps * rows / e2e_s, "unit": "rows/s", "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * 4},
+        "gpu_launches": run.launches * args.steps,
+        "forward": {"dense_weight_bytes_per_step": dense,
+                    "expert_weight_bytes_per_step_upper_bound": int(cfg.layers * touched * per_expert),
+                    "weight_roofline_ms_upper_bound": (dense + cfg.layers * touched * per_expert) / (peak * 1e6), "peak_kind": kind}}))
 
 
 def leave_group():
@@ -202,7 +289,10 @@ def main():
                     help="skip the prefill: set the context length directly (KV pages and recurrent state stay zero); for profiler runs")
     ap.add_argument("--no-spinup", action="store_true", help="skip the half second of untimed steps that brings the clocks up")
     ap.add_argument("--exchange", default="peer", help="tensor-parallel exchange: 'peer' (own kernel over NVLink peer memory) or 'nccl'")
-    ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit")
+    ap.add_argument("--model", default="dense27b", help="'dense27b' (the headline workload) or 'moe30b': the 30B-A3B-class "
+                    "mixture-of-experts hybrid (group 32, 128 experts top-8 + shared) on a ragged batch of 32 sequences")
+    ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit; "
+                    "'prefill': the same for the tcgen05 prefill-width matmul")
     ap.add_argument("--shape", default="17408x5120")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=4, help="--only qmm: weight copies rotated through (4 x 50 MB > L2)")
@@ -247,8 +337,13 @@ def main():
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
 
-    if args.only == "qmm":
+    if args.only in ("qmm", "prefill"):
         return only_qmm(args, dev)
+
+    if args.model == "moe30b":
+        if world > 1:
+            raise SystemExit("the mixture-of-experts model runs on one GPU in this build (expert parallelism is not built)")
+        return bench_moe(args, dev)
 
     spec = dict(synthetic.DENSE_27B, layers=args.layers)
     cfg = F.Config(**spec)

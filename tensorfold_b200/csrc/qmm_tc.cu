@@ -128,7 +128,7 @@ constexpr int kWorkers = 148;
 constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every row bucket, so that the
                                 // K segments (hence the bits) do not depend on the row count
 constexpr int kCols = 128;      // columns per column block = TMEM lanes = tensor-core M
-constexpr int kThreads = 11 * 32;
+constexpr int kThreads = 15 * 32;   // 4 dequantisers, 4 epilogue, producer, MMA issuer, finisher, 4 more epilogue (128-row bucket)
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 4096 + 512 * (64 / group); }
 __host__ __device__ constexpr int pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
@@ -150,6 +150,8 @@ struct Cfg {
     static constexpr int SSG = KTS * GPT * NC;             // (group, chunk) pairs per stage
     static constexpr int USG = SSG / UPS;                  // pairs per unit
     static constexpr int AU = 2, DU = 2;
+    static constexpr int ESETS = NC;                       // epilogue warp sets: one per row chunk (two in the 128-row bucket)
+    static_assert(ESETS == 1 || (USG == 1 && UPS % 2 == 0), "with two epilogue sets, units alternate between the row chunks");
     static constexpr int NBARS = 2 * STAGES + 2 * AU + 2 * DU;
     static constexpr int SMEM = STAGES * STAGE_BYTES + NBARS * 8 + 128;
     static constexpr int A_COLS = AU * KTS * 16;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
     if (threadIdx.x == 0) {
         // a stage is free when the 4 dequantiser warps and the 4 epilogue warps are done with it; the epilogue
         // warps arrive only after the tensor core's last unit of the stage completed, so its reads are over too
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 8); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4 + 4 * C::ESETS); }
         for (int s = 0; s < AU; ++s) { mbar_init(a_full(s), 4); mbar_init(a_empty(s), 4); }
         for (int s = 0; s < DU; ++s) { mbar_init(d_full(s), 1); mbar_init(d_empty(s), 4); }
         mbar_fence_init();
@@ -434,11 +436,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
         // ------------------- finisher: sums parked segments while the others go on ----------------
         pdl_wait();
         if (part_first) {
-            named_bar_sync(2, 5 * 32);
+            named_bar_sync(2, (4 * C::ESETS + 1) * 32);
             finish_segment(a, cb_first, SPB, total, lane, seg_list);
         }
         if (part_last) {
-            named_bar_sync(3, 5 * 32);
+            named_bar_sync(3, (4 * C::ESETS + 1) * 32);
             finish_segment(a, cb_last, SPB, total, lane, seg_list);
         }
     } else if (warp < 4) {
@@ -475,24 +477,32 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
             ar.next();
             stage.next();
         }
-    } else {
+    } else if (warp < 8 || C::ESETS == 2) {
         // ------------------- epilogue warps: products from tensor memory -> fp32 scale/bias -> output ----------
+        // A warp reads the 32 tensor-memory lanes (columns) of its quadrant q = warp % 4. In the 128-row
+        // bucket there are two sets of four warps, one per 64-row chunk: units alternate between the chunks,
+        // so set c always drains accumulator slot c, and each thread holds 64 sums, not 128.
         pdl_wait();
-        const int q = warp - 4, col_local = q * 32 + lane;
+        constexpr bool SPLIT = C::ESETS == 2;
+        constexpr int ACC = NB / C::ESETS;
+        const int set = SPLIT ? (warp >= 11 ? 1 : 0) : 0, row0 = set * ACC;
+        const int q = warp & 3, col_local = q * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16) + C::D_COL0;
         Ring stage(STAGES, 0), dr(DU, 0), ar(AU, 0);
-        float acc[NB];
+        if (SPLIT) dr.i = set;
+        float acc[ACC];
         StageWalk<KTS> wk(begin, end, SPB, KT);
         while (wk.valid()) {
             const int cb = wk.cb, seg_begin = wk.it;
 #pragma unroll
-            for (int n = 0; n < NB; ++n) acc[n] = 0.f;
+            for (int n = 0; n < ACC; ++n) acc[n] = 0.f;
             while (wk.valid() && wk.cb == cb) {
                 const int ngroups = wk.nkt() * C::GPT;
                 mbar_wait(full_bar(stage.i), stage.phase, a.status);
                 const uint8_t* wst = stage0 + stage.i * C::STAGE_BYTES;
 #pragma unroll
                 for (int u = 0; u < UPS; ++u) {
+                    if (SPLIT && (u & 1) != set) continue;            // the other set's unit
                     mbar_wait(d_full(dr.i), dr.phase, a.status);
                     tc_fence_after();
                     if (u == UPS - 1) {                   // the stage's last unit is done: the tensor core has read all of its A operand
@@ -530,8 +540,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
                                 for (int b = 0; b < BATCH; ++b)
 #pragma unroll
                                     for (int i4 = 0; i4 < 4; ++i4) {
-                                        const int n = chunk * C::RB + (p0 + b) * 16 + i4 * 4;
-                                        const float4 xs = xs4[n / 4], un = un4[n / 4];
+                                        const int nn = chunk * C::RB + (p0 + b) * 16 + i4 * 4, n = nn - (SPLIT ? chunk * C::RB : 0);
+                                        const float4 xs = xs4[nn / 4], un = un4[nn / 4];
                                         acc[n + 0] = __fmaf_rn(bi, xs.x, __fmaf_rn(sc, (hi[b][i4 * 4 + 0] + lo[b][i4 * 4 + 0]) * un.x, acc[n + 0]));
                                         acc[n + 1] = __fmaf_rn(bi, xs.y, __fmaf_rn(sc, (hi[b][i4 * 4 + 1] + lo[b][i4 * 4 + 1]) * un.y, acc[n + 1]));
                                         acc[n + 2] = __fmaf_rn(bi, xs.z, __fmaf_rn(sc, (hi[b][i4 * 4 + 2] + lo[b][i4 * 4 + 2]) * un.z, acc[n + 2]));
@@ -540,7 +550,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
                             }
                         }
                     }
-                    dr.next();
+                    if (SPLIT) dr.phase ^= 1;             // this set's slot comes round again after the other set's unit
+                    else dr.next();
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar(stage.i));
@@ -555,10 +566,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
             if (whole) {
                 if (col < a.N) {
 #pragma unroll
-                    for (int n = 0; n < NB; ++n) {
-                        if (n < a.M) {
-                            if (a.f32_out) reinterpret_cast<float*>(a.y)[(size_t)n * a.N + col] = acc[n];
-                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)n * a.N + col] = f2bf(acc[n]);
+                    for (int n = 0; n < ACC; ++n) {
+                        if (row0 + n < a.M) {
+                            if (a.f32_out) reinterpret_cast<float*>(a.y)[(size_t)(row0 + n) * a.N + col] = acc[n];
+                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)(row0 + n) * a.N + col] = f2bf(acc[n]);
                         }
                     }
                 }
@@ -566,11 +577,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const Args a) {
                 // slot 2*cta + 1 when this CTA entered the column block from an earlier one, else 2*cta
                 float* slot = a.slots + (size_t)(2 * blockIdx.x + (begin < cb_begin ? 1 : 0)) * kSlotFloats;
 #pragma unroll
-                for (int n = 0; n < NB; ++n)
-                    if (n < a.M) __stcg(slot + n * kCols + col_local, acc[n]);
+                for (int n = 0; n < ACC; ++n)
+                    if (row0 + n < a.M) __stcg(slot + (row0 + n) * kCols + col_local, acc[n]);
                 // hand over to the finisher warp without waiting for it
-                if (cb == cb_first) asm volatile("bar.arrive 2, %0;" ::"r"(5 * 32) : "memory");
-                else asm volatile("bar.arrive 3, %0;" ::"r"(5 * 32) : "memory");
+                if (cb == cb_first) asm volatile("bar.arrive 2, %0;" ::"r"((4 * C::ESETS + 1) * 32) : "memory");
+                else asm volatile("bar.arrive 3, %0;" ::"r"((4 * C::ESETS + 1) * 32) : "memory");
             }
         }
     }
