@@ -155,3 +155,33 @@ def test_copy_drafter_and_digest():
     assert accept_path([10, 11], [5, 5]) == 1
     a, b = DecodeResult([[1, 2], [3]], 0.0, 1), DecodeResult([[1, 2], [3]], 1.0, 2)
     assert a.sha256() == b.sha256() != DecodeResult([[1, 2, 3]], 0.0, 1).sha256()
+
+
+def test_checkpoint_roundtrip_keeps_every_array(tmp_path):
+    """safetensors + config.json under the reference's tensor names (weights.py:151-198) -> the stored model."""
+
+    from oracle import lane_oracle as O
+    from tensorfold_b200 import weights
+
+    cfg = O.Config(hidden=256, intermediate=512, layers=4, heads=4, kv_heads=2, head_dim=128, vocab=512, k_heads=2, v_heads=4,
+                   dk=128, dv=128)
+    model = O.random_model(cfg, 3)
+    weights.save(model, tmp_path)
+    got = weights.load(tmp_path)
+    c = got["config"]
+    assert (c.hidden, c.layers, c.heads, c.kv_heads, c.k_heads, c.v_heads, c.group, c.rope_dims) == (256, 4, 4, 2, 2, 4, 64, 32)
+    for a, b in zip(model["layers"], got["layers"]):
+        assert a["linear"] == b["linear"]
+        for name, va in a.items():
+            vb = b[name]
+            if hasattr(va, "words"):
+                assert torch.equal(va.words, vb.words) and torch.equal(va.scales, vb.scales) and torch.equal(va.biases, vb.biases)
+            elif torch.is_tensor(va):
+                assert torch.equal(va.float(), vb.float()), name
+    assert torch.equal(model["head"].words, got["head"].words) and torch.equal(model["embed"].scales, got["embed"].scales)
+    import safetensors.torch as st_
+    tensors = st_.load_file(str(tmp_path / "model.safetensors"))
+    tensors["model.layers.0.unknown.weight"] = torch.zeros(1)
+    st_.save_file(tensors, str(tmp_path / "model.safetensors"))
+    with pytest.raises(ValueError):
+        weights.load(tmp_path)
