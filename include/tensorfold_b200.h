@@ -48,10 +48,11 @@ int tf_qmm_workers(void);
  *   y[m, n] = round_bf16( sum over groups g in order of  s[n,g] * (x[m, g-block] . q[n, g-block])
  *                                                       + b[n,g] * xs[m,g] )
  *
- * x_packed: the M input rows (1..128) in packed form — per 64-input k tile, Mp = M rounded up to 4
- *          rows of 128 bytes, then the tile's group sums [64/group][Mp] fp32; tf_packed_bytes bytes,
- *          16-byte aligned. tf_pack_rows builds it from row-major bf16; the glue kernels below
- *          write it directly.
+ * x_packed: the M input rows (1..128) in packed form: per 64-input k tile, Mp rows of 128 bytes (Mp = M
+ *          rounded up to its bucket 8, 16, 32, 64 or 128; rows past M zero; 16-byte chunk c of row r
+ *          stored at chunk c ^ 4*(r&1)), then the tile's group sums [64/group][Mp] fp32;
+ *          tf_packed_bytes bytes, 16-byte aligned. tf_pack_rows builds it from row-major bf16; the glue
+ *          kernels below write it directly.
  * w_tiled: weights in this library's tile layout (tf_qmm_tiled_bytes / tf_qmm_tile below).
  * y  [M, N] bf16 (fp32 with TF_QMM_F32_OUT).  group is 64 or 32.  K a multiple of 64.
  * scratch: tf_qmm_scratch_bytes() bytes, 256-byte aligned; its first TF_QMM_COUNTER_BYTES bytes

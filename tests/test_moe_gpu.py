@@ -106,3 +106,34 @@ def test_grouped_projection_has_the_bits_of_the_lane_matmul(setup):
                 continue
             want = lane_qmm.lane_matmul(x[code // 32:code // 32 + 1], gate_up)
             assert_same_bits(buf.gate_up[p, j:j + 1], want, f"problem {p} member {j}")
+
+
+def test_matches_fp32_at_the_reference_test_shape(lib):
+    """The reference's own MoE check (tests/cuda/test_flashnext_kernels.py:124-144) on this library: 64 experts,
+    top 10 + shared, expert width 640, hidden 2560; picks are the (logit desc, id asc) order of the fp32 logits
+    and every slot's output is within max|y| * 2^-5 + 1e-3 of the fp32 computation."""
+
+    from tensorfold_b200 import lane_moe
+
+    gen = torch.Generator().manual_seed(6)
+    e, k, d, inter = 64, 10, 2560, 640
+    gates = [O.random_q4(gen, inter, d, G) for _ in range(e + 1)]
+    ups = [O.random_q4(gen, inter, d, G) for _ in range(e + 1)]
+    downs = [O.random_q4(gen, d, inter, G) for _ in range(e + 1)]
+    router_rows = (torch.randn((e + 1, d), generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.randn((3, d), generator=gen).to(torch.bfloat16)
+    ex = lane_moe.make_experts(gates, ups, downs, G)
+    buf = lane_moe.MoEBuffers(3, e, k, True, d, inter, G, "cuda")
+    lane_moe.moe(x.cuda(), router_rows.cuda(), ex, buf)
+    torch.cuda.synchronize()
+    xf = x.float()
+    logits = xf @ router_rows.float().T
+    y, loc, pick = buf.y.cpu(), buf.pair_loc.cpu(), buf.pick.cpu()
+    for r in range(3):
+        top = sorted(range(e), key=lambda i: (-logits[r, i].item(), i))[:k]
+        assert pick[r, :k].tolist() == top and int(pick[r, k]) == e
+        for slot, i in enumerate(top + [e]):
+            gw, uw, dw = (O.dequantize(q.words, q.scales, q.biases, G) for q in (gates[i], ups[i], downs[i]))
+            want = (torch.nn.functional.silu(xf[r] @ gw.T) * (xf[r] @ uw.T)) @ dw.T
+            err = (y[int(loc[r, slot])] - want).abs().max().item()
+            assert err <= want.abs().max().item() * 2 ** -5 + 1e-3, (r, slot, err)
