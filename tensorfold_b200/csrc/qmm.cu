@@ -29,7 +29,7 @@
 // are again one contiguous range.
 //
 // Warp roles in a CTA: 16 consumer warps (one 16-column tile each), one producer thread (bulk
-// copies), three finisher warps that sum parked K segments so the consumers never wait on a fence.
+// copies), one finisher warp that sums parked K segments so the consumers never wait on a fence.
 
 #include "common.cuh"
 
@@ -41,7 +41,6 @@ constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every
                                 // K segments (hence the bits) do not depend on the row count
 constexpr int kWarps = 16;      // consumer warps = column tiles per column block (baked into the layout)
 constexpr int kCols = kWarps * 16;
-constexpr int kFinishWarps = 3; // finisher warps (20 warps a CTA keeps 96 registers a thread): sum parked K segments while the consumers stream on
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 512 + (64 / group) * 64; }
 
@@ -59,7 +58,7 @@ struct Cfg {
     static constexpr int W_BYTES = kWarps * KTS * REC;
     static constexpr int X_BYTES = KTS * XTILE;
     static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + 127) / 128) * 128;
-    static constexpr int THREADS = (kWarps + 1 + kFinishWarps) * 32;   // consumers + producer warp + finisher warps
+    static constexpr int THREADS = (kWarps + 2) * 32;   // consumers + producer warp + finisher warp
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
 };
 
@@ -95,7 +94,7 @@ constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
 template <int NT>
 __device__ __forceinline__ void group_sync() {
     if (NT == 32) __syncwarp();
-    else named_bar_sync(NT == kFinishWarps * 32 ? 4 : 1, NT);     // the finisher group and the consumers have a barrier each
+    else named_bar_sync(1, NT);
 }
 
 template <int NT>
@@ -168,7 +167,7 @@ __device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total
 }
 
 template <int G, int MB, int KTS, int STAGES>
-__global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kernel(const Args a) {
+__global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a) {
     using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
     extern __shared__ __align__(128) uint8_t smem[];
@@ -200,13 +199,9 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
 
     // the first and the last segment of this CTA's range may be parts of a column block
     const int cb_first = begin < end ? begin / SPB : 0, cb_last = begin < end ? (end - 1) / SPB : 0;
-    // Order of work inside a range that spans several column blocks: the partial segment at its END
-    // first, then the rest from the beginning. Both partial segments of a worker are thus parked early
-    // and summed by the finisher warps while the consumers stream whole blocks, so the kernel's tail is
-    // plain output writes, not a park-ticket-sum chain. (Which k tiles form a segment does not change.)
-    // A range inside one block is a single partial segment; the consumers sum it themselves.
-    const bool single = cb_first == cb_last;
-    const int t0 = (!single && end < (cb_last + 1) * SPB) ? cb_last * SPB : end;   // start of the trailing partial segment
+    // a partial segment that ends the range is summed by the consumers themselves; one that starts a
+    // longer range goes to the finisher warp
+    const bool part_first = cb_last != cb_first && begin > cb_first * SPB;
 
     if (warp == kWarps) {
         // ------------------------------- producer: one thread ----------------------------------
@@ -215,16 +210,13 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
         if (lane == 0 && begin < end) {
             int s = 0, issued = 0;
             uint32_t phase = 1;
-            int early_kt0[STAGES], early_nkt[STAGES];
-            bool waited = multi;
-            for (int pass = 0; pass < 2; ++pass) {
-            const int r0 = pass ? begin : t0, r1 = pass ? t0 : end;
-            if (r0 >= r1) continue;
-            int gb = r0 / SPB, st = r0 - gb * SPB;
+            int gb = cb_first, st = begin - gb * SPB;
             int prob = gb / CB, cb = gb - prob * CB;
             const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[prob] * a.w_stride : 0);
             const uint8_t* xbase = a.xp + (size_t)prob * a.xp_stride;
-            for (int it = r0; it < r1; ++it) {
+            int early_kt0[STAGES], early_nkt[STAGES];
+            bool waited = multi;
+            for (int it = begin; it < end; ++it) {
                 for (int sub = 0; sub < kItemTiles; sub += KTS) {
                     const int kt0 = st * kItemTiles + sub, nkt = min(KTS, KT - kt0);
                     if (nkt <= 0) break;
@@ -251,11 +243,10 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
                     if (++cb == CB) {
                         cb = 0;
                         ++prob;
-                        if (multi && it + 1 < r1) wbase = a.w + (size_t)a.prob_expert[prob] * a.w_stride;
+                        if (multi && it + 1 < end) wbase = a.w + (size_t)a.prob_expert[prob] * a.w_stride;
                         xbase = a.xp + (size_t)prob * a.xp_stride;
                     }
                 }
-            }
             }
             if (!waited) {
                 pdl_wait();
@@ -268,16 +259,11 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
     }
     pdl_wait();                  // everything below reads or writes what other kernels produce or read
     if (begin >= end) return;
-    if (warp > kWarps) {
-        // ------------------- finishers: sum parked segments while the consumers go on -----------
-        const int ftid = threadIdx.x - (kWarps + 1) * 32;
-        if (!single && t0 < end) {
-            named_bar_sync(3, (kWarps + kFinishWarps) * 32);
-            finish_segment<kFinishWarps * 32>(a, cb_last, CB, SPB, total, ftid, seg_list[0]);
-        }
-        if (!single && begin > cb_first * SPB) {
-            named_bar_sync(2, (kWarps + kFinishWarps) * 32);
-            finish_segment<kFinishWarps * 32>(a, cb_first, CB, SPB, total, ftid, seg_list[0]);
+    if (warp == kWarps + 1) {
+        // ------------------- finisher: sums parked segments while the consumers go on -----------
+        if (part_first) {
+            named_bar_sync(2, (kWarps + 1) * 32);
+            finish_segment<32>(a, cb_first, CB, SPB, total, lane, seg_list[0]);
         }
         return;
     }
@@ -288,13 +274,11 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
     float acc[MB][4];
     int s = 0;
     uint32_t phase = 0;
-    for (int pass = 0; pass < 2; ++pass) {
-    const int r1 = pass ? t0 : end;
-    int it = pass ? begin : t0;
-    while (it < r1) {
+    int it = begin;
+    while (it < end) {
         const int gb = it / SPB, prob = gb / CB, cb = gb - prob * CB;
         const int cb_begin = gb * SPB, cb_end = cb_begin + SPB;
-        const int seg_begin = it, seg_end = cb_end < r1 ? cb_end : r1;
+        const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
         for (int rb = 0; rb < MB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
 
@@ -378,11 +362,9 @@ __global__ void __launch_bounds__((kWarps + 1 + kFinishWarps) * 32, 1) qmm_kerne
                     const int row = rb * 8 + 2 * t + (i & 1);
                     if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
                 }
-            if (single) finish_segment<kWarps * 32>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
-            else if (pass == 0) asm volatile("bar.arrive 3, %0;" ::"r"((kWarps + kFinishWarps) * 32) : "memory");   // the finishers take it; go on
-            else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + kFinishWarps) * 32) : "memory");
+            if (seg_end == end) finish_segment<kWarps * 32>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
+            else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");   // the finisher takes it; go on
         }
-    }
     }
 }
 
