@@ -67,14 +67,16 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
 
 /* Grouped form for mixture-of-experts layers: up to max_probs independent problems of 8 rows each in
  * one launch. Problem p multiplies its packed rows (x_packed + p * tf_packed_bytes(8, K, group)) with
- * the weight of expert prob_expert[p] (w_tiled + e * tf_qmm_tiled_bytes(N, K, group): the experts'
- * tiled weights stacked) into y + p * 8 * N elements. The number of live problems is read on the
- * device from prob_count[0] (clamped to max_probs), so a captured step serves any routing. A row's
- * result is that of tf_qmm on the same row and weight: the arithmetic is the 8-row bucket's always.
+ * weight slot prob_expert[p] (w_tiled + slot * tf_qmm_tiled_bytes(N, K, group): the experts' tiled
+ * weights stacked) into y + p * 8 * N elements. The number of live problems is read on the device from
+ * prob_count[0] (clamped to max_probs), so a captured step serves any routing. With prob_sel not NULL
+ * the launch covers problems prob_sel[0 .. prob_count[0]) only (an expert-parallel rank's own
+ * experts), still addressed by their own index p. A row's result is that of tf_qmm on the same row and
+ * weight: the arithmetic is the 8-row bucket's always.
  * Replaces: families/qwen4_exp/cuda/qmm.py:421-602 (Experts, Group, moe_gateup, moe_down). */
-int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count, int max_probs,
-                   void* y, void* scratch, size_t scratch_bytes, int N, int K, int group, int flags, int* status,
-                   void* stream);
+int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count,
+                   const int* prob_sel, int max_probs, void* y, void* scratch, size_t scratch_bytes, int N, int K, int group,
+                   int flags, int* status, void* stream);
 
 /* Row-major bf16 rows x [M, K] -> packed rows with their group sums; when xs is not NULL the sums
  * are also written as [M, K/group] fp32. A group's sum is formed in eights: eight (group 64) or four
@@ -269,17 +271,32 @@ int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, voi
  * tf_moe_act: compact gate/up results [problem, 8, 2 I] bf16 -> bf16(silu(gate) * up), packed for the
  *   down projection of the same problems.
  * tf_moe_combine: out[r] = bf16(sum over slots, in slot order, of wts[r, k] * y[pair_loc[r, k]]) with
- *   y the compact fp32 down results [problem * 8 + place, D]; fma, one rounding. */
+ *   y the compact fp32 down results [problem * 8 + place, D]; fma, one rounding.
+ * Expert parallelism (world > 1; no counterpart in the reference, which shards expert width instead):
+ *   every rank routes all rows and builds the same list; routed expert e belongs to rank
+ *   e / (experts / world) as local weight slot e % (experts / world), the shared expert is replicated
+ *   as local slot experts / world with its problems dealt round-robin. tf_moe_group then also writes
+ *   prob_sel (this rank's problems, ascending) and sel_count, and prob_expert holds local slots: pass
+ *   prob_sel / sel_count to tf_qmm_grouped. tf_moe_push stores the rank's results as 16-byte packets
+ *   {value, n, value, n} into EVERY rank's buffer (peer_bufs as for tf_peer_exchange; a slot is
+ *   max_probs * 8 * D * 8 bytes, zero before first use) at the problem's own index; tf_moe_combine_peer
+ *   polls the packets its pairs need (bounded, TF_ESTALL) and combines as tf_moe_combine does - the
+ *   result has the bits of the one-GPU block. seq and tickets as for tf_peer_exchange; consecutive
+ *   exchanges alternate between two slots. */
 int tf_moe_max_problems(int rows, int slots, int experts_total);
 int tf_moe_router(const void* x, size_t x_stride, const void* router, float* logits, int rows, int D, int experts_total,
                   void* stream);
 int tf_moe_select(const float* logits, int rows, int experts_total, int experts, int top_k, int* pick, float* wts, void* stream);
 int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int max_probs, int* prob_expert, int* prob_count,
-                 int* prob_rows, int* pair_loc, void* stream);
+                 int* prob_rows, int* pair_loc, int experts, int rank, int world, int* prob_sel, int* sel_count, void* stream);
 int tf_moe_pack(const void* x, size_t x_stride, const int* prob_rows, const int* prob_count, int max_probs, void* x_packed, int K,
                 int group, void* stream);
 int tf_moe_act(const void* gate_up, const int* prob_count, int max_probs, void* act_packed, int I, int group, void* stream);
 int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* stream);
+int tf_moe_push(const float* y, const int* prob_sel, const int* sel_count, int max_probs, int D, void* const* peer_bufs,
+                size_t slot_off, int world, const void* seq, void* stream);
+int tf_moe_combine_peer(const void* packets, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* seq,
+                        void* tickets, int* status, void* stream);
 
 /* ---- tensor-parallel exchange over peer memory ---------------------------------------------------
  * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (gather_rank_partials over NCCL) and the

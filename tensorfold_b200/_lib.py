@@ -28,8 +28,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p]),
-    "tf_qmm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_int, c_int,
-                               c_int, c_int, c_void_p, c_void_p]),
+    "tf_qmm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_int,
+                               c_int, c_int, c_int, c_void_p, c_void_p]),
     "tf_pack_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_qmm_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -71,7 +71,11 @@ SIGNATURES: dict[str, tuple] = {
     "tf_moe_max_problems": (c_int, [c_int, c_int, c_int]),
     "tf_moe_router": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_moe_select": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "tf_moe_group": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tf_moe_group": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_void_p, c_void_p, c_void_p]),
+    "tf_moe_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
+    "tf_moe_combine_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                    c_void_p]),
     "tf_moe_pack": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_act": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),

@@ -101,22 +101,10 @@ __global__ void __launch_bounds__(32) moe_select_kernel(const float* logits, int
 }
 
 // ---- problem list: one CTA, one thread per expert id ----------------------------------------------
-__global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R, int slots, int NE, int max_probs, int* prob_expert,
-                                                         int* prob_count, int* prob_rows, int* pair_loc) {
-    extern __shared__ int sh_pick[];             // R * slots picks
-    __shared__ int warp_tot[33];
-    pdl_launch_dependents();
-    pdl_wait();
-    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
-    const int pairs = R * slots;
-    for (int i = e; i < pairs; i += 1024) sh_pick[i] = pick[i];
-    __syncthreads();
-    int cnt = 0;
-    if (e < NE)
-        for (int i = 0; i < pairs; ++i) cnt += sh_pick[i] == e;
-    const int mine = (cnt + 7) >> 3;             // problems of this expert
-    // exclusive prefix sum over expert ids (fixed order)
-    int inc = mine;
+// exclusive prefix sum of one int per thread over the CTA's 1024 threads, fixed order
+__device__ int scan1024(int v, int* warp_tot, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const int n = __shfl_up_sync(0xffffffffu, inc, o);
@@ -135,10 +123,46 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R,
         if (lane == 31) warp_tot[32] = winc;
     }
     __syncthreads();
-    const int base = warp_tot[warp] + inc - mine, total = min(warp_tot[32], max_probs);
+    const int base = warp_tot[warp] + inc - v;
+    total = warp_tot[32];
+    __syncthreads();
+    return base;
+}
+
+// Expert parallelism (world > 1): routed expert e lives on rank e / (E / world) as local weight slot
+// e % (E / world); the shared expert (id E) is replicated as local slot E / world and its problems
+// are dealt round-robin. Every rank builds the same global list and, besides, the ascending list
+// prob_sel of the problems it owns; prob_expert then holds LOCAL weight slots (meaningful for owned
+// problems only).
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R, int slots, int NE, int max_probs, int* prob_expert,
+                                                         int* prob_count, int* prob_rows, int* pair_loc, int E, int rank, int world,
+                                                         int* prob_sel, int* sel_count) {
+    extern __shared__ int sh_pick[];             // R * slots picks
+    __shared__ int warp_tot[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = threadIdx.x;
+    const int pairs = R * slots;
+    for (int i = e; i < pairs; i += 1024) sh_pick[i] = pick[i];
+    __syncthreads();
+    int cnt = 0;
+    if (e < NE)
+        for (int i = 0; i < pairs; ++i) cnt += sh_pick[i] == e;
+    const int mine = (cnt + 7) >> 3;             // problems of this expert
+    int all;
+    const int base = scan1024(mine, warp_tot, all);
+    const int total = min(all, max_probs);
     if (e == 0) prob_count[0] = total;
+    const int per = world > 1 ? E / world : 0;
+    const bool shared = e >= E;
+    // problems of this expert owned by this rank: all or none for a routed expert, every world-th for the shared one
+    int owned = 0;
+    if (world > 1 && e < NE) owned = shared ? (mine + world - 1 - rank) / world : (e / per == rank ? mine : 0);
+    int all_owned = 0;
+    const int sel_base = world > 1 ? scan1024(owned, warp_tot, all_owned) : 0;
+    if (world > 1 && e == 0) sel_count[0] = all_owned;      // owned problems never exceed max_probs: they are a subset
     if (e < NE && cnt > 0) {
-        int j = 0;
+        int j = 0, sel = sel_base;
         for (int i = 0; i < pairs; ++i) {
             if (sh_pick[i] != e) continue;
             const int p = base + (j >> 3);
@@ -146,7 +170,14 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R,
                 const int row = i / slots, slot = i - row * slots;
                 prob_rows[p * 8 + (j & 7)] = row * kMaxSlots + slot;
                 pair_loc[i] = p * 8 + (j & 7);
-                if ((j & 7) == 0) prob_expert[p] = e;
+                if ((j & 7) == 0) {
+                    if (world == 1) {
+                        prob_expert[p] = e;
+                    } else {
+                        prob_expert[p] = shared ? per : e % per;
+                        if (shared ? ((j >> 3) % world == rank) : (e / per == rank)) prob_sel[sel++] = p;
+                    }
+                }
             }
             ++j;
         }
@@ -224,6 +255,77 @@ __global__ void moe_combine_kernel(const float* y, const int* pair_loc, const fl
     *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
 }
 
+// ---- expert parallelism: results of a rank's own problems to every rank, then the combine --------------
+// Packets as in the tensor-parallel exchange: 16 bytes {value, n, value, n}, n = the exchange number. A
+// problem has one owner, so every rank's buffer is one array indexed like the compact results
+// ([problem * 8 + place][D / 2] packets) and nobody writes another's entries. The combine polls exactly
+// the packets its pairs need (bounded) and adds a row's slots in slot order, as on one GPU.
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_volatile16(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__global__ void __launch_bounds__(256) moe_push_kernel(const float2* y, const int* prob_sel, const int* sel_count, int D2,
+                                                       uint8_t* const* bufs, size_t slot_off, int world, const uint32_t* seq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(seq) + 1u;
+    const int n = sel_count[0];
+    for (int q = blockIdx.y; q < n; q += gridDim.y) {
+        const size_t base = (size_t)prob_sel[q] * 8 * D2;
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 8 * D2; i += gridDim.x * blockDim.x) {
+            const float2 v = y[base + i];
+            const uint4 pkt = make_uint4(__float_as_uint(v.x), want, __float_as_uint(v.y), want);
+            for (int peer = 0; peer < world; ++peer) st_volatile16(reinterpret_cast<uint4*>(bufs[peer] + slot_off) + base + i, pkt);
+        }
+    }
+}
+
+constexpr unsigned kPollLimit = 1u << 24;
+
+__global__ void moe_combine_peer_kernel(const uint4* packets, const int* pair_loc, const float* wts, int slots, __nv_bfloat16* out, int R,
+                                        int D, uint32_t* seq, int* tickets, int* status) {
+    __shared__ int is_last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t want = *reinterpret_cast<volatile uint32_t*>(seq) + 1u;
+    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;       // c: a pair of packets = 4 values
+    if (c < (D >> 2) && r < R) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        bool stalled = false;
+        for (int k = 0; k < slots; ++k) {
+            const float w = wts[(size_t)r * slots + k];
+            const uint4* src = packets + (size_t)pair_loc[r * slots + k] * (D >> 1) + 2 * c;
+            uint4 a = ld_volatile16(src), b = ld_volatile16(src + 1);
+            unsigned spins = 0;
+            while ((a.y != want || a.w != want || b.y != want || b.w != want) && !stalled) {
+                if (++spins > kPollLimit) { stalled = true; break; }
+                a = ld_volatile16(src);
+                b = ld_volatile16(src + 1);
+            }
+            acc.x = __fmaf_rn(w, __uint_as_float(a.x), acc.x);
+            acc.y = __fmaf_rn(w, __uint_as_float(a.z), acc.y);
+            acc.z = __fmaf_rn(w, __uint_as_float(b.x), acc.z);
+            acc.w = __fmaf_rn(w, __uint_as_float(b.z), acc.w);
+        }
+        if (stalled) report(status, TF_ESTALL);
+        __nv_bfloat16* o = out + (size_t)r * D + 4 * c;
+        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc.x, acc.y);
+        *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(tickets, 1) == (int)(gridDim.x * gridDim.y) - 1;
+    __syncthreads();
+    if (is_last && threadIdx.x == 0) {
+        *tickets = 0;
+        *reinterpret_cast<volatile uint32_t*>(seq) = want;
+    }
+}
+
 }  // namespace
 }  // namespace tf
 
@@ -254,11 +356,14 @@ int tf_moe_select(const float* logits, int rows, int experts_total, int experts,
 }
 
 int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int max_probs, int* prob_expert, int* prob_count,
-                 int* prob_rows, int* pair_loc, void* stream) {
+                 int* prob_rows, int* pair_loc, int experts, int rank, int world, int* prob_sel, int* sel_count, void* stream) {
     if (rows < 1 || rows > 128 || slots < 1 || slots > tf::kMaxSlots || experts_total < 1 || experts_total > tf::kMaxExperts + 1) return TF_EINVAL;
     if (max_probs < 1 || !pick || !prob_expert || !prob_count || !prob_rows || !pair_loc) return TF_EINVAL;
+    if (world < 1 || rank < 0 || rank >= world || experts < 1 || experts > experts_total) return TF_EINVAL;
+    if (world > 1 && (experts % world || !prob_sel || !sel_count)) return TF_EINVAL;
     size_t smem = (size_t)rows * slots * sizeof(int);
-    void* args[] = {&pick, &rows, &slots, &experts_total, &max_probs, &prob_expert, &prob_count, &prob_rows, &pair_loc};
+    void* args[] = {&pick, &rows, &slots, &experts_total, &max_probs, &prob_expert, &prob_count, &prob_rows, &pair_loc,
+                    &experts, &rank, &world, &prob_sel, &sel_count};
     return tf::launch_pdl((const void*)tf::moe_group_kernel, dim3(1), dim3(1024), smem, static_cast<cudaStream_t>(stream), args) ==
                    cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }
@@ -289,6 +394,32 @@ int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int sl
     if (((uintptr_t)y | (uintptr_t)out) & 15) return TF_EALIGN;
     void* args[] = {&y, &pair_loc, &wts, &slots, &out, &rows, &D};
     return tf::launch_pdl((const void*)tf::moe_combine_kernel, dim3((D / 4 + 255) / 256, rows), dim3(256), 0,
+                          static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_push(const float* y, const int* prob_sel, const int* sel_count, int max_probs, int D, void* const* peer_bufs,
+                size_t slot_off, int world, const void* seq, void* stream) {
+    if (max_probs < 1 || D < 4 || D % 4 || world < 2 || world > 64 || !y || !prob_sel || !sel_count || !peer_bufs || !seq) return TF_EINVAL;
+    if (((uintptr_t)y | slot_off) & 15) return TF_EALIGN;
+    const float2* src = reinterpret_cast<const float2*>(y);
+    int d2 = D / 2;
+    uint8_t* const* bufs = reinterpret_cast<uint8_t* const*>(peer_bufs);
+    const uint32_t* seq_p = static_cast<const uint32_t*>(seq);
+    int by = max_probs < 64 ? max_probs : 64;
+    void* args[] = {&src, &prob_sel, &sel_count, &d2, &bufs, &slot_off, &world, &seq_p};
+    return tf::launch_pdl((const void*)tf::moe_push_kernel, dim3(2, by), dim3(256), 0, static_cast<cudaStream_t>(stream), args) ==
+                   cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
+}
+
+int tf_moe_combine_peer(const void* packets, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* seq,
+                        void* tickets, int* status, void* stream) {
+    if (rows < 1 || rows > 65535 || slots < 1 || D < 8 || D % 8 || !packets || !pair_loc || !wts || !out || !seq || !tickets) return TF_EINVAL;
+    if (((uintptr_t)packets | (uintptr_t)out) & 15) return TF_EALIGN;
+    const uint4* pk = static_cast<const uint4*>(packets);
+    uint32_t* seq_p = static_cast<uint32_t*>(seq);
+    int* tick_p = static_cast<int*>(tickets);
+    void* args[] = {&pk, &pair_loc, &wts, &slots, &out, &rows, &D, &seq_p, &tick_p, &status};
+    return tf::launch_pdl((const void*)tf::moe_combine_peer_kernel, dim3((D / 4 + 255) / 256, rows), dim3(256), 0,
                           static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }
 

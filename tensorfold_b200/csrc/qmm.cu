@@ -74,8 +74,11 @@ struct Args {
     // grouped form (MoE experts): `max_probs` problems of 8 rows each, problem p multiplying its own
     // packed rows (xp + p * xp_stride) with the weight of expert prob_expert[p] (w + e * w_stride)
     // into y + p * y_stride elements; the live count is read on the device. nullptr: one problem.
+    // With prob_sel, the launch covers the problems prob_sel[0 .. count) only (an expert-parallel rank's
+    // own experts); addresses are still formed from the selected problem's index.
     const int* prob_expert;
     const int* prob_count;
+    const int* prob_sel;
     int max_probs;
     long long w_stride, xp_stride, y_stride;
 };
@@ -102,7 +105,8 @@ __device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total
     __threadfence();
     group_sync<NT>();
     const int cb_begin = gb * SPB;
-    const int prob = gb / CB, cb = gb - prob * CB;
+    const int q = gb / CB, cb = gb - q * CB;
+    const int prob = a.prob_sel ? a.prob_sel[q] : q;
     if (tid == 0) {
         const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
         int nseg = 0;
@@ -175,8 +179,11 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K >> 6;                              // k tiles
     const int CB = (a.N + kCols - 1) / kCols;             // column blocks
-    const int SPB = (KT + kItemTiles - 1) / kItemTiles;   // schedule items per column block
     const bool multi = a.prob_expert != nullptr;
+    // Grouped launches never cut a column block along K: where the cut falls would depend on how many
+    // problems the launch holds, that is on the other rows' routing. One item = a whole (problem, block).
+    const int item_tiles = multi ? ((KT + KTS - 1) / KTS) * KTS : kItemTiles;
+    const int SPB = (KT + item_tiles - 1) / item_tiles;   // schedule items per column block
     if (multi) pdl_wait();                                // the problem list is the previous kernel's output
     const int probs = multi ? min(*a.prob_count, a.max_probs) : 1;
     const int total = probs * CB * SPB;                   // "column block" below: (problem, column block) pairs
@@ -212,13 +219,14 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
             uint32_t phase = 1;
             int gb = cb_first, st = begin - gb * SPB;
             int prob = gb / CB, cb = gb - prob * CB;
-            const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[prob] * a.w_stride : 0);
-            const uint8_t* xbase = a.xp + (size_t)prob * a.xp_stride;
+            auto picked = [&](int q) { return a.prob_sel ? a.prob_sel[q] : q; };
+            const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[picked(prob)] * a.w_stride : 0);
+            const uint8_t* xbase = a.xp + (size_t)picked(prob) * a.xp_stride;
             int early_kt0[STAGES], early_nkt[STAGES];
             bool waited = multi;
             for (int it = begin; it < end; ++it) {
-                for (int sub = 0; sub < kItemTiles; sub += KTS) {
-                    const int kt0 = st * kItemTiles + sub, nkt = min(KTS, KT - kt0);
+                for (int sub = 0; sub < item_tiles; sub += KTS) {
+                    const int kt0 = st * item_tiles + sub, nkt = min(KTS, KT - kt0);
                     if (nkt <= 0) break;
                     if (issued == STAGES && !waited) {
                         pdl_wait();
@@ -243,8 +251,10 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     if (++cb == CB) {
                         cb = 0;
                         ++prob;
-                        if (multi && it + 1 < end) wbase = a.w + (size_t)a.prob_expert[prob] * a.w_stride;
-                        xbase = a.xp + (size_t)prob * a.xp_stride;
+                        if (multi && it + 1 < end) {
+                            wbase = a.w + (size_t)a.prob_expert[picked(prob)] * a.w_stride;
+                            xbase = a.xp + (size_t)picked(prob) * a.xp_stride;
+                        }
                     }
                 }
             }
@@ -276,15 +286,16 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     uint32_t phase = 0;
     int it = begin;
     while (it < end) {
-        const int gb = it / SPB, prob = gb / CB, cb = gb - prob * CB;
+        const int gb = it / SPB, cb = gb - (gb / CB) * CB;
+        const int prob = a.prob_sel ? a.prob_sel[gb / CB] : gb / CB;
         const int cb_begin = gb * SPB, cb_end = cb_begin + SPB;
         const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
         for (int rb = 0; rb < MB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
 
         for (; it < seg_end; ++it)
-        for (int sub = 0; sub < kItemTiles; sub += KTS) {
-            const int nkt = min(KTS, KT - ((it - cb_begin) * kItemTiles + sub));
+        for (int sub = 0; sub < item_tiles; sub += KTS) {
+            const int nkt = min(KTS, KT - ((it - cb_begin) * item_tiles + sub));
             if (nkt <= 0) break;
             mbar_wait(full_bar(s), phase, a.status);
             const uint8_t* sb = stage0 + s * C::STAGE_BYTES;
@@ -536,21 +547,21 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
     a.status = status;
     a.M = M; a.N = N; a.K = K;
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
-    a.prob_expert = nullptr; a.prob_count = nullptr; a.max_probs = 1;
+    a.prob_expert = nullptr; a.prob_count = nullptr; a.prob_sel = nullptr; a.max_probs = 1;
     a.w_stride = a.xp_stride = a.y_stride = 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return group == 64 ? tf::dispatch<64>(a, st) : tf::dispatch<32>(a, st);
 }
 
-int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count, int max_probs,
-                   void* y, void* scratch, size_t scratch_bytes, int N, int K, int group, int flags, int* status,
+int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count,
+                   const int* prob_sel, int max_probs, void* y, void* scratch, size_t scratch_bytes, int N, int K, int group, int flags, int* status,
                    void* stream) {
     if (max_probs < 1 || N < 1 || K < 64 || K % 64) return TF_EINVAL;
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
     if (!x_packed || !w_tiled || !y || !prob_expert || !prob_count) return TF_EINVAL;
-    const long long CB = (N + tf::kCols - 1) / tf::kCols, SPB = (K / 64 + tf::kItemTiles - 1) / tf::kItemTiles;
-    if (CB * max_probs * 4 > TF_QMM_COUNTER_BYTES || CB * SPB * max_probs > (1 << 30) / tf::kWorkers) return TF_EINVAL;
+    const long long CB = (N + tf::kCols - 1) / tf::kCols;     // one schedule item per (problem, column block)
+    if (CB * max_probs * 4 > TF_QMM_COUNTER_BYTES || CB * max_probs > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
     if ((uintptr_t)y & 3) return TF_EALIGN;
     if (!scratch || ((uintptr_t)scratch & 255)) return TF_ESCRATCH;
@@ -564,7 +575,7 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.status = status;
     a.M = 8; a.N = N; a.K = K;
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
-    a.prob_expert = prob_expert; a.prob_count = prob_count; a.max_probs = max_probs;
+    a.prob_expert = prob_expert; a.prob_count = prob_count; a.prob_sel = prob_sel; a.max_probs = max_probs;
     a.w_stride = (long long)tf_qmm_tiled_bytes(N, K, group);
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;

@@ -137,3 +137,23 @@ def test_matches_fp32_at_the_reference_test_shape(lib):
             want = (torch.nn.functional.silu(xf[r] @ gw.T) * (xf[r] @ uw.T)) @ dw.T
             err = (y[int(loc[r, slot])] - want).abs().max().item()
             assert err <= want.abs().max().item() * 2 ** -5 + 1e-3, (r, slot, err)
+
+
+def test_rows_alone_at_a_shape_with_more_work_items_than_workers(lib):
+    """Hidden 2048, expert width 768, 64 rows x 9 slots: hundreds of (problem, column block) items over 148
+    workers. A grouped launch must not cut a block along K (the cut would move with the other rows' routing)."""
+
+    from tensorfold_b200 import lane_moe
+
+    gen = torch.Generator().manual_seed(12)
+    e, k, d, inter = 32, 8, 2048, 768
+    gates = [O.random_q4(gen, inter, d, G) for _ in range(e + 1)]
+    ups = [O.random_q4(gen, inter, d, G) for _ in range(e + 1)]
+    downs = [O.random_q4(gen, d, inter, G) for _ in range(e + 1)]
+    router_rows = (torch.randn((e + 1, d), generator=gen) * 0.02).to(torch.bfloat16).cuda()
+    ex = lane_moe.make_experts(gates, ups, downs, G)
+    x = torch.randn((64, d), generator=gen).to(torch.bfloat16).cuda()
+    out = lane_moe.moe(x, router_rows, ex, lane_moe.MoEBuffers(64, e, k, True, d, inter, G, "cuda")).clone()
+    for rows in (1, 5, 33):
+        part = lane_moe.moe(x[:rows], router_rows, ex, lane_moe.MoEBuffers(rows, e, k, True, d, inter, G, "cuda"))
+        assert_same_bits(part, out[:rows], f"first {rows} rows alone vs inside 64 rows")

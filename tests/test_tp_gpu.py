@@ -30,3 +30,17 @@ def test_window_rows_equal_serial_steps_under_tp(lib, world, exchange):
     assert m.group(2) == "1", "window rows differ from the same ranks' serial decode"
     assert m.group(3) == "1", "vocabulary-split draw differs from the whole-vocabulary draw"
     assert float(m.group(4)) > 0.999          # the reference's cross-world bound (tests/cuda/test_flashnext_tp.py:218-227)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_block_has_the_bits_of_one_gpu(lib, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29460 + world), str(ROOT / "tests" / "ep_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = re.search(r"EP_RESULT world=(\d+) equals_one_gpu=(\d)", out.stdout)
+    assert m and int(m.group(1)) == world, out.stdout[-2000:]
+    assert m.group(2) == "1", "the expert-parallel block differs from the one-GPU block"
