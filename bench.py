@@ -188,19 +188,23 @@ def only_qmm(args, dev):
                       "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
 
 
-def bench_moe(args, dev):
-    """BASELINE config 4 on one GPU: 48-layer MoE hybrid, 32 sequences with draft widths uniform in 1..8
-    (redrawn until they fit the 128-row forward) and contexts uniform in 1k..16k. The context is set
-    synthetically (zero KV pages and recurrent state: same kernels, same traffic)."""
+def bench_moe(args, dev, rank=0, world=1):
+    """BASELINE config 4: 48-layer MoE hybrid, 32 sequences with draft widths uniform in 1..8 (redrawn until
+    they fit the 128-row forward) and contexts uniform in 1k..16k. The context is set synthetically (zero
+    KV pages and recurrent state: same kernels, same traffic). With N ranks the experts are spread over
+    the ranks (expert parallelism); attention, GDN and routing are replicated."""
 
     import random
 
     import torch
 
-    from tensorfold_b200 import _lib, forward as F, runner, synthetic
+    from tensorfold_b200 import _lib, forward as F, lane_moe, runner, synthetic
 
     cfg = F.Config(**dict(synthetic.MOE_30B, layers=min(args.layers, 48)))
-    w = synthetic.random_weights(cfg, seed=2, device=dev)
+    ep = None
+    if world > 1:
+        ep = lane_moe.ExpertGroup(cfg.experts, cfg.top_k, cfg.shared_expert, cfg.hidden, dev)
+    w = synthetic.random_weights(cfg, seed=2, device=dev, expert_ids=ep.local_experts(cfg.shared_expert) if ep else None)
     rng = random.Random(11)
     seqs = 32
     widths = [rng.randint(1, 8) for _ in range(seqs)]
@@ -209,7 +213,7 @@ def bench_moe(args, dev):
     ctxs = [rng.randint(1024, 16384) for _ in range(seqs)]
     rows = sum(widths)
     st = F.State(w, seqs, max(ctxs) + 16, dev)
-    run = runner.LaneRunner(w, st, widths, max_context=max(ctxs) + 8)
+    run = runner.LaneRunner(w, st, widths, max_context=max(ctxs) + 8, ep=ep)
     run.capture()
     st.lens = list(ctxs)
     run.refresh()
@@ -221,23 +225,38 @@ def bench_moe(args, dev):
     while time.time() < t_end:
         run.step_device()
         torch.cuda.synchronize(dev)
-    torch.cuda.synchronize(dev)
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(dev.index or 0) as clk:
         e0.record()
         for _ in range(args.steps):
             run.step_device()
         e1.record()
-        torch.cuda.synchronize(dev)
-    ms = e0.elapsed_time(e1)
-    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32)
-    torch.cuda.synchronize(dev)
+        barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32, generator=torch.Generator().manual_seed(13))   # every rank feeds the same tokens
+    barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         run.step(host_tokens)
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
     _lib.status(dev).raise_if_set()
+    if rank != 0:
+        leave_group()
+        return
     peak, kind = peaks()
     g = cfg.group
     bits = 0.5 + 4.0 / g
@@ -245,19 +264,23 @@ def bench_moe(args, dev):
     per_expert = (3 * cfg.moe_intermediate * cfg.hidden) * bits
     touched = min(cfg.experts, rows * cfg.top_k) + 1          # upper bound of distinct experts a layer streams
     print(json.dumps({
-        "metric": "lane-verify rows/sec", "value": args.steps * rows / (ms / 1000.0), "unit": "rows/s", "n_gpus": 1,
+        "metric": "lane-verify rows/sec", "value": args.steps * rows / (ms / 1000.0), "unit": "rows/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"MoE hybrid 30B-A3B-class 4-bit g32 verify forward: {cfg.layers} layers, hidden 2048, 128 experts top-8 + "
                                f"shared, expert width 768; 32 sequences, draft widths uniform 1..8 ({rows} rows), contexts uniform 1k..16k "
-                               "(set synthetically)", "seqs": seqs, "rows": rows, "parallelism": "single GPU",
+                               "(set synthetically)", "seqs": seqs, "rows": rows,
+                   "parallelism": "single GPU" if world == 1 else f"ep{world} (experts over ranks, the rest replicated)",
                    "l2": "weights streamed per forward exceed the 126 MB L2; no flush needed"},
         "clocks": clk.summary(),
         "e2e": {"value": args.steps * rows / e2e_s, "unit": "rows/s", "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * 4},
         "gpu_launches": run.launches * args.steps,
         "forward": {"dense_weight_bytes_per_step": dense,
                     "expert_weight_bytes_per_step_upper_bound": int(cfg.layers * touched * per_expert),
-                    "weight_roofline_ms_upper_bound": (dense + cfg.layers * touched * per_expert) / (peak * 1e6), "peak_kind": kind}}))
+                    "weight_roofline_ms_upper_bound": (dense + cfg.layers * touched * per_expert) / (peak * 1e6), "peak_kind": kind}}),
+          flush=True)
+    if world > 1:
+        leave_group()
 
 
 def leave_group():
@@ -333,7 +356,8 @@ def main():
         from tensorfold_b200 import distributed
 
         dist.init_process_group("nccl", device_id=dev)
-        tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
+        if args.model != "moe30b":
+            tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
 
@@ -341,9 +365,7 @@ def main():
         return only_qmm(args, dev)
 
     if args.model == "moe30b":
-        if world > 1:
-            raise SystemExit("the mixture-of-experts model runs on one GPU in this build (expert parallelism is not built)")
-        return bench_moe(args, dev)
+        return bench_moe(args, dev, rank, world)
 
     spec = dict(synthetic.DENSE_27B, layers=args.layers)
     cfg = F.Config(**spec)
@@ -398,7 +420,7 @@ def main():
     value = args.steps * rows / (ms / 1000.0)
 
     # ---- end to end through the public call: host tokens in, chosen tokens out, every step ----
-    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32)
+    host_tokens = torch.randint(0, cfg.vocab, (rows,), dtype=torch.int32, generator=torch.Generator().manual_seed(13))   # every rank feeds the same tokens
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):

@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const float2* y, const in
     }
 }
 
-constexpr unsigned kPollLimit = 1u << 24;
+constexpr unsigned kPollLimit = 1u << 22;
 
 __global__ void moe_combine_peer_kernel(const uint4* packets, const int* pair_loc, const float* wts, int slots, __nv_bfloat16* out, int R,
                                         int D, uint32_t* seq, int* tickets, int* status) {
@@ -296,7 +296,8 @@ __global__ void moe_combine_peer_kernel(const uint4* packets, const int* pair_lo
     const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;       // c: a pair of packets = 4 values
     if (c < (D >> 2) && r < R) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        bool stalled = false;
+        // once a wait has run out anywhere in this process the exchange is lost: do not wait again
+        bool stalled = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
         for (int k = 0; k < slots; ++k) {
             const float w = wts[(size_t)r * slots + k];
             const uint4* src = packets + (size_t)pair_loc[r * slots + k] * (D >> 1) + 2 * c;

@@ -25,7 +25,7 @@
 namespace tf {
 namespace {
 
-constexpr unsigned kSpinLimit = 1u << 24;     // polls of one packet (each a memory round trip): seconds, then TF_ESTALL
+constexpr unsigned kSpinLimit = 1u << 22;     // polls of one packet (each a memory round trip): seconds, then TF_ESTALL
 
 __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local,
             st_volatile16(reinterpret_cast<uint4*>(bufs[peer] + slot_off) + (size_t)rank * n2 + i, pkt);
     }
     const uint4* mine = reinterpret_cast<const uint4*>(bufs[rank] + slot_off);
-    bool stalled = false;
+    // once a wait has run out anywhere in this process the exchange is lost: do not wait again
+    bool stalled = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
     for (int r = 0; r < world; ++r) {
         for (int i = first; i < n2; i += stride) {
             uint4 pkt = ld_volatile16(mine + (size_t)r * n2 + i);

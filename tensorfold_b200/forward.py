@@ -241,7 +241,7 @@ class Record:
 
 @torch.no_grad()
 def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_logits: bool = True,
-                 max_chunks: int | None = None, batch: Batch | None = None, tp=None):
+                 max_chunks: int | None = None, batch: Batch | None = None, tp=None, ep=None):
     """Logits (rows, vocab) bf16 for the window rows, and the record ``commit`` needs.
 
     ``windows``: one window width per sequence of ``st`` (packed rows are each sequence's chain in
@@ -250,6 +250,8 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     ``tp``: a ``distributed.RankGroup`` when ``w`` is one rank's shard: the output and down projections
     then return fp32 partials, every rank gathers all of them and the next norm adds them in rank order
     (two collectives a layer); the logits are this rank's slice of the vocabulary.
+    ``ep``: a ``lane_moe.ExpertGroup`` when the MoE layers' experts are spread over ranks (``w`` then holds
+    this rank's experts; everything else is replicated and every rank computes the same rows).
     """
 
     c = w.config
@@ -326,7 +328,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
         r, rparts = row_parallel(mixed, layer.out_proj)
         if layer.experts is not None:
             x, hrows = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts, rows_out=True, packed_out=False)
-            pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf), None
+            pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf, ep), None
             continue
         x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts)
         gu = lane_matmul(h, layer.gate_up, out=mlp_in)

@@ -19,8 +19,8 @@ from .forward import Batch, Record, State, Weights, commit, make_batch, refresh_
 
 
 class LaneRunner:
-    def __init__(self, w: Weights, st: State, widths: Sequence[int], *, max_context: int, sampling=None, tp=None):
-        self.w, self.st, self.tp, self.sampling = w, st, tp, sampling
+    def __init__(self, w: Weights, st: State, widths: Sequence[int], *, max_context: int, sampling=None, tp=None, ep=None):
+        self.w, self.st, self.tp, self.ep, self.sampling = w, st, tp, ep, sampling
         dev = w.norm.device
         self.device = dev
         for s, wd in enumerate(widths):
@@ -41,7 +41,7 @@ class LaneRunner:
         self.launches = 0
 
     def _body(self):
-        self.logits, self.record = tree_forward(self.w, self.tokens, None, self.st, batch=self.batch, tp=self.tp)
+        self.logits, self.record = tree_forward(self.w, self.tokens, None, self.st, batch=self.batch, tp=self.tp, ep=self.ep)
         if self.tp is None:
             self.chosen = exact_sampling.sample_rows(self.logits, self.positions, self.sampling)
         else:

@@ -24,9 +24,11 @@ def random_q4(gen: torch.Generator, n: int, k: int, group: int, device, spread: 
     return tile_weight(words, scales, biases, group)
 
 
-def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, world: int = 1) -> Weights:
+def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, world: int = 1, expert_ids=None) -> Weights:
     """Weights of ``cfg`` from ``seed``; with ``world`` > 1, the tensor-parallel shard of ``rank``
-    (heads and MLP width split; see ``distributed.shard_config``)."""
+    (heads and MLP width split; see ``distributed.shard_config``). ``expert_ids``: for expert
+    parallelism, the global ids of the experts to create (``ExpertGroup.local_experts``); an expert's
+    weights depend on (seed, layer, id) only, so every world size sees the same experts."""
 
     from .distributed import shard_config
 
@@ -49,10 +51,15 @@ def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, wor
         if cfg.experts:
             ne = cfg.experts + (1 if cfg.shared_expert else 0)
             gate_up = down = None
-            gu = [random_q4(gen, 2 * cfg.moe_intermediate, cfg.hidden, g, device).tiled for _ in range(ne)]
-            dn = [random_q4(gen, cfg.hidden, cfg.moe_intermediate, g, device).tiled for _ in range(ne)]
-            extra = dict(router=(0.05 * torch.randn((ne, cfg.hidden), generator=gen, device=device)).to(bf),
-                         experts=Experts(torch.cat(gu), torch.cat(dn), ne, cfg.hidden, cfg.moe_intermediate, g))
+            ids = list(range(ne)) if expert_ids is None else list(expert_ids)
+            gu, dn = [], []
+            egen = torch.Generator(device=device)
+            for e in ids:
+                egen.manual_seed((seed * 1000 + i) * 4096 + e + 1)
+                gu.append(random_q4(egen, 2 * cfg.moe_intermediate, cfg.hidden, g, device).tiled)
+                dn.append(random_q4(egen, cfg.hidden, cfg.moe_intermediate, g, device).tiled)
+            extra = dict(router=(0.05 * torch.randn((ne, cfg.hidden), generator=rgen, device=device)).to(bf),
+                         experts=Experts(torch.cat(gu), torch.cat(dn), len(ids), cfg.hidden, cfg.moe_intermediate, g))
         else:
             gate_up = random_q4(gen, 2 * sc.intermediate, cfg.hidden, g, device)
             down = random_q4(gen, cfg.hidden, sc.intermediate, g, device)
