@@ -100,13 +100,13 @@ __device__ __forceinline__ void group_sync() {
     else named_bar_sync(1, NT);
 }
 
-template <int NT>
+template <int NT, bool MULTI>
 __device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total, int tid, int* list) {
     __threadfence();
     group_sync<NT>();
     const int cb_begin = gb * SPB;
-    const int q = gb / CB, cb = gb - q * CB;
-    const int prob = a.prob_sel ? a.prob_sel[q] : q;
+    const int q = MULTI ? gb / CB : 0, cb = gb - q * CB;
+    const int prob = (MULTI && a.prob_sel) ? a.prob_sel[q] : q;
     if (tid == 0) {
         const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
         int nseg = 0;
@@ -170,7 +170,7 @@ __device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total
     if (tid == 0) a.counters[gb] = 0;      // leave the counters zero for the next call (every reader is past its ticket)
 }
 
-template <int G, int MB, int KTS, int STAGES>
+template <int G, int MB, int KTS, int STAGES, bool MULTI>
 __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a) {
     using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
@@ -179,10 +179,10 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K >> 6;                              // k tiles
     const int CB = (a.N + kCols - 1) / kCols;             // column blocks
-    const bool multi = a.prob_expert != nullptr;
+    constexpr bool multi = MULTI;      // the grouped form is its own instantiation: the plain one pays nothing for it
     // Grouped launches never cut a column block along K: where the cut falls would depend on how many
     // problems the launch holds, that is on the other rows' routing. One item = a whole (problem, block).
-    const int item_tiles = multi ? ((KT + KTS - 1) / KTS) * KTS : kItemTiles;
+    const int item_tiles = multi ? ((KT + KTS - 1) / KTS) * KTS : kItemTiles;   // a constant in the plain form
     const int SPB = (KT + item_tiles - 1) / item_tiles;   // schedule items per column block
     if (multi) pdl_wait();                                // the problem list is the previous kernel's output
     const int probs = multi ? min(*a.prob_count, a.max_probs) : 1;
@@ -218,8 +218,8 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
             int s = 0, issued = 0;
             uint32_t phase = 1;
             int gb = cb_first, st = begin - gb * SPB;
-            int prob = gb / CB, cb = gb - prob * CB;
-            auto picked = [&](int q) { return a.prob_sel ? a.prob_sel[q] : q; };
+            int prob = MULTI ? gb / CB : 0, cb = gb - prob * CB;
+            auto picked = [&](int q) { return (MULTI && a.prob_sel) ? a.prob_sel[q] : q; };
             const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[picked(prob)] * a.w_stride : 0);
             const uint8_t* xbase = a.xp + (size_t)picked(prob) * a.xp_stride;
             int early_kt0[STAGES], early_nkt[STAGES];
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
         // ------------------- finisher: sums parked segments while the consumers go on -----------
         if (part_first) {
             named_bar_sync(2, (kWarps + 1) * 32);
-            finish_segment<32>(a, cb_first, CB, SPB, total, lane, seg_list[0]);
+            finish_segment<32, MULTI>(a, cb_first, CB, SPB, total, lane, seg_list[0]);
         }
         return;
     }
@@ -286,8 +286,8 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     uint32_t phase = 0;
     int it = begin;
     while (it < end) {
-        const int gb = it / SPB, cb = gb - (gb / CB) * CB;
-        const int prob = a.prob_sel ? a.prob_sel[gb / CB] : gb / CB;
+        const int gb = it / SPB, pq = MULTI ? gb / CB : 0, cb = gb - pq * CB;
+        const int prob = (MULTI && a.prob_sel) ? a.prob_sel[pq] : pq;
         const int cb_begin = gb * SPB, cb_end = cb_begin + SPB;
         const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
@@ -373,17 +373,17 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     const int row = rb * 8 + 2 * t + (i & 1);
                     if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
                 }
-            if (seg_end == end) finish_segment<kWarps * 32>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
+            if (seg_end == end) finish_segment<kWarps * 32, MULTI>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
             else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");   // the finisher takes it; go on
         }
     }
 }
 
-template <int G, int MB, int KTS, int STAGES>
+template <int G, int MB, int KTS, int STAGES, bool MULTI = false>
 int launch(const Args& a, cudaStream_t stream) {
     using C = Cfg<G, MB, KTS, STAGES>;
     static_assert(C::SMEM <= 227 * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<G, MB, KTS, STAGES>;
+    auto kern = qmm_kernel<G, MB, KTS, STAGES, MULTI>;
     static bool configured = false;   // per instantiation; the attribute is per function and idempotent
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
@@ -580,7 +580,8 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return group == 64 ? tf::launch<64, 1, 4, tf::stages_for<64, 1, 4>()>(a, st) : tf::launch<32, 1, 4, tf::stages_for<32, 1, 4>()>(a, st);
+    return group == 64 ? tf::launch<64, 1, 4, tf::stages_for<64, 1, 4>(), true>(a, st)
+                       : tf::launch<32, 1, 4, tf::stages_for<32, 1, 4>(), true>(a, st);
 }
 
 int tf_qmm_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,
