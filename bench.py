@@ -4,7 +4,7 @@
 
 A step is one verify forward (all 64 layers + head + token choice) over S sequences x W drafted rows
 with C committed tokens of context each; weights are random 4-bit group-64 of the 27B-class
-architecture (BASELINE config 3), prompts random token ids, the context built by real prefill through
+architecture, prompts random token ids, the context built by real prefill through
 the same kernels. Prints ONE JSON line (rank 0). With N > 1 the model is tensor-parallel over N ranks
 (launch under torchrun). ``--impl reference`` times the CPU restatement of the reference arithmetic
 (``oracle/``) on the host cores for the same workload, on a bounded sample.
@@ -189,7 +189,7 @@ def only_qmm(args, dev):
 
 
 def bench_moe(args, dev, rank=0, world=1):
-    """BASELINE config 4: 48-layer MoE hybrid, 32 sequences with draft widths uniform in 1..8 (redrawn until
+    """The 30B-A3B-class workload: 48-layer MoE hybrid, 32 sequences with draft widths uniform in 1..8 (redrawn until
     they fit the 128-row forward) and contexts uniform in 1k..16k. The context is set synthetically (zero
     KV pages and recurrent state: same kernels, same traffic). With N ranks the experts are spread over
     the ranks (expert parallelism); attention, GDN and routing are replicated."""
