@@ -227,17 +227,38 @@ __global__ void attn_merge_kernel(const float* part_o, const float* part_m, cons
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    for (int c = 0; c < nch; ++c) {
-        const size_t base = ((size_t)c * R + row) * H + head;
-        const float cm = part_m[base], cl = part_l[base];
-        if (!(cl > 0.f)) continue;
-        const float mn = fmaxf(m, cm);
-        const float sa = exp2f(m - mn), sb = exp2f(cm - mn);       // m = -inf gives sa = 0
-        const float* po = part_o + base * D + lane * PER;
+    // chunks are read four at a time (independent loads in flight together) and applied one by one in
+    // chunk order, so the arithmetic is that of the plain sequential merge
+    constexpr int B = 4;
+    static_assert(PER % 4 == 0, "a lane's slice is whole 16-byte loads");
+    for (int c0 = 0; c0 < nch; c0 += B) {
+        float cm[B], cl[B];
+        float4 po[B][PER / 4];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) acc[i] = acc[i] * sa + po[i] * sb;
-        l = l * sa + cl * sb;
-        m = mn;
+        for (int j = 0; j < B; ++j) {
+            const int c = min(c0 + j, nch - 1);
+            const size_t base = ((size_t)c * R + row) * H + head;
+            cm[j] = part_m[base];
+            cl[j] = c0 + j < nch ? part_l[base] : 0.f;
+            const float4* src = reinterpret_cast<const float4*>(part_o + base * D + lane * PER);
+#pragma unroll
+            for (int i = 0; i < PER / 4; ++i) po[j][i] = src[i];
+        }
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            if (!(cl[j] > 0.f)) continue;
+            const float mn = fmaxf(m, cm[j]);
+            const float sa = exp2f(m - mn), sb = exp2f(cm[j] - mn);       // m = -inf gives sa = 0
+#pragma unroll
+            for (int i = 0; i < PER / 4; ++i) {
+                acc[4 * i + 0] = acc[4 * i + 0] * sa + po[j][i].x * sb;
+                acc[4 * i + 1] = acc[4 * i + 1] * sa + po[j][i].y * sb;
+                acc[4 * i + 2] = acc[4 * i + 2] * sa + po[j][i].z * sb;
+                acc[4 * i + 3] = acc[4 * i + 3] * sa + po[j][i].w * sb;
+            }
+            l = l * sa + cl[j] * sb;
+            m = mn;
+        }
     }
     __nv_bfloat16* dst = out + ((size_t)row * H + head) * D + lane * PER;
 #pragma unroll

@@ -171,7 +171,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // Kernels can be launched with programmatic stream serialisation: a kernel may then become resident
 // while its predecessor still runs, do its input-independent work (barrier setup, weight prefetch)
 // and block in pdl_wait() until the predecessor's memory is visible. TF_PDL in the environment
-// selects who gets the attribute: bit 0 the small kernels, bit 1 the matmuls. Measured on the 27B
+// selects who gets the attribute: bit 0 the small kernels, bit 1 the matmuls, bit 2 the norm kernel. Measured on the 27B
 // forward (16-layer slice, ms a step): 0: 2.17, 1: 2.18, 2: 2.01 -> 1.92, 3: 2.01; early-resident small
 // kernels cost more than their hidden launch latency saves, so the default is 2 (matmuls only).
 // Without the attribute pdl_wait() and pdl_launch_dependents() do nothing.
@@ -179,9 +179,10 @@ inline int pdl_mode() {
     static const int mode = [] { const char* e = std::getenv("TF_PDL"); return e ? (e[0] - '0') : 2; }();
     return mode;
 }
-inline bool pdl_enabled(bool matmul = false) { return (pdl_mode() & (matmul ? 2 : 1)) != 0; }
+// kind: 0 a small kernel, 1 a matmul, 2 the residual-add + norm that feeds a matmul
+inline bool pdl_enabled(int kind = 0) { return (pdl_mode() >> kind) & 1; }
 
-inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args) {
+inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args, int kind = 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -191,7 +192,7 @@ inline cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kind) ? 1 : 0;
     return cudaLaunchKernelExC(&cfg, fn, args);
 }
 

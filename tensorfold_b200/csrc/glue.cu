@@ -305,7 +305,7 @@ int tf_norm_xs(const void* x, const void* residual, const void* partials, int np
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* args[] = {&x, &residual, &partials, &nparts, &part_stride, &weight, &h_out, &y_rows, &y_packed, &M, &D, &eps};
     const void* fn = group == 64 ? (const void*)tf::norm_xs_kernel<64> : (const void*)tf::norm_xs_kernel<32>;
-    return tf::finish(tf::launch_pdl(fn, dim3(y_packed ? tf::tf_padded_rows(M) : M), dim3(D / 8), 0, st, args));
+    return tf::finish(tf::launch_pdl(fn, dim3(y_packed ? tf::tf_padded_rows(M) : M), dim3(D / 8), 0, st, args, 2));
 }
 
 int tf_swiglu(const void* gate, const void* up, size_t in_stride, void* out_packed, void* out_rows, int M, int I,

@@ -616,7 +616,7 @@ int launch(const Args& a, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled(true) ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(1) ? 1 : 0;
     if (cudaLaunchKernelEx(&cfg, kern, a) != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
 }
