@@ -316,7 +316,7 @@ int tf_swiglu(const void* gate, const void* up, size_t in_stride, void* out_pack
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* args[] = {&gate, &up, &in_stride, &out_packed, &out_rows, &M, &I};
     const void* fn = group == 64 ? (const void*)tf::swiglu_kernel<64> : (const void*)tf::swiglu_kernel<32>;
-    return tf::finish(tf::launch_pdl(fn, dim3((I / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args));
+    return tf::finish(tf::launch_pdl(fn, dim3((I / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args, 3));
 }
 
 int tf_gated_norm(const void* y, const void* z, size_t z_stride, const void* weight, void* out_packed, void* out_rows,
@@ -327,7 +327,7 @@ int tf_gated_norm(const void* y, const void* z, size_t z_stride, const void* wei
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* args[] = {&y, &z, &z_stride, &weight, &out_packed, &out_rows, &M, &v_heads, &eps};
     const void* fn = group == 64 ? (const void*)tf::gated_norm_kernel<64> : (const void*)tf::gated_norm_kernel<32>;
-    return tf::finish(tf::launch_pdl(fn, dim3((v_heads * 16 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args));
+    return tf::finish(tf::launch_pdl(fn, dim3((v_heads * 16 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args, 3));
 }
 
 int tf_gate_mul(const void* o, const void* qg, size_t qg_stride, void* out_packed, void* out_rows, int M, int heads,
@@ -338,7 +338,7 @@ int tf_gate_mul(const void* o, const void* qg, size_t qg_stride, void* out_packe
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* args[] = {&o, &qg, &qg_stride, &out_packed, &out_rows, &M, &heads, &head_dim};
     const void* fn = group == 64 ? (const void*)tf::gate_mul_kernel<64> : (const void*)tf::gate_mul_kernel<32>;
-    return tf::finish(tf::launch_pdl(fn, dim3((heads * head_dim / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args));
+    return tf::finish(tf::launch_pdl(fn, dim3((heads * head_dim / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args, 3));
 }
 
 int tf_attn_prep(const void* qg, size_t qg_stride, const void* k, size_t k_stride, const void* v, size_t v_stride,
@@ -352,7 +352,7 @@ int tf_attn_prep(const void* qg, size_t qg_stride, const void* k, size_t k_strid
     void* args[] = {&qg, &qg_stride, &k, &k_stride, &v, &v_stride, &q_norm, &k_norm, &row_pos, &inv_freq, &rope_half,
                     &q_out, &k_out, &v_out, &heads, &kv_heads, &head_dim, &eps};
     return tf::finish(tf::launch_pdl((const void*)tf::attn_prep_kernel, dim3((total + warps - 1) / warps, M),
-                                     dim3(warps * 32), warps * head_dim * sizeof(float), static_cast<cudaStream_t>(stream), args));
+                                     dim3(warps * 32), warps * head_dim * sizeof(float), static_cast<cudaStream_t>(stream), args, 3));
 }
 
 int tf_gdn_pre(const void* qkv, size_t qkv_stride, const void* conv_state, const void* conv_w, const int* row_seq,
@@ -367,7 +367,7 @@ int tf_gdn_pre(const void* qkv, size_t qkv_stride, const void* conv_state, const
     void* args[] = {&qkv, &qkv_stride, &conv_state, &conv_w, &row_seq, &row_idx, &a, &b, &ab_stride, &a_log, &dt_bias,
                     &q_out, &k_out, &v_out, &g_out, &beta_out, &k_heads, &v_heads};
     return tf::finish(tf::launch_pdl((const void*)tf::gdn_pre_kernel, dim3((total + warps - 1) / warps, M), dim3(warps * 32),
-                                     0, static_cast<cudaStream_t>(stream), args));
+                                     0, static_cast<cudaStream_t>(stream), args, 3));
 }
 
 int tf_embed(const int* ids, const void* words, const void* scales, const void* biases, void* out, int M, int D, int group,
