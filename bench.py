@@ -357,7 +357,15 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
         if args.model != "moe30b":
-            tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
+            try:
+                tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
+            except Exception as exc:      # no symmetric memory between these GPUs: the library collective still works
+                if args.exchange != "peer":
+                    raise
+                print(f"bench: peer exchange unavailable ({type(exc).__name__}: {exc}); using the NCCL all-gather", file=sys.stderr)
+                args.exchange = "nccl"
+                tp = distributed.RankGroup(exchange="nccl")
+            config["parallelism"] = f"tp{world} ({args.exchange} exchange)"
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
 
