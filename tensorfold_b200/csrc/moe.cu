@@ -137,17 +137,23 @@ __device__ int scan1024(int v, int* warp_tot, int& total) {
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R, int slots, int NE, int max_probs, int* prob_expert,
                                                          int* prob_count, int* prob_rows, int* pair_loc, int E, int rank, int world,
                                                          int* prob_sel, int* sel_count) {
-    extern __shared__ int sh_pick[];             // R * slots picks
+    extern __shared__ __align__(16) int sh_pick[];   // R * slots picks, padded to a multiple of four
     __shared__ int warp_tot[33];
     pdl_launch_dependents();
     pdl_wait();
     const int e = threadIdx.x;
-    const int pairs = R * slots;
-    for (int i = e; i < pairs; i += 1024) sh_pick[i] = pick[i];
+    const int pairs = R * slots, pairs4 = (pairs + 3) >> 2;      // the picks are scanned four at a time (padded with -1)
+    for (int i = e; i < pairs4 * 4; i += 1024) sh_pick[i] = i < pairs ? pick[i] : -1;
     __syncthreads();
+    const int4* pk4 = reinterpret_cast<const int4*>(sh_pick);
     int cnt = 0;
-    if (e < NE)
-        for (int i = 0; i < pairs; ++i) cnt += sh_pick[i] == e;
+    if (e < NE) {
+#pragma unroll 4
+        for (int i = 0; i < pairs4; ++i) {
+            const int4 v = pk4[i];
+            cnt += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+        }
+    }
     const int mine = (cnt + 7) >> 3;             // problems of this expert
     int all;
     const int base = scan1024(mine, warp_tot, all);
@@ -163,8 +169,14 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R,
     if (world > 1 && e == 0) sel_count[0] = all_owned;      // owned problems never exceed max_probs: they are a subset
     if (e < NE && cnt > 0) {
         int j = 0, sel = sel_base;
-        for (int i = 0; i < pairs; ++i) {
-            if (sh_pick[i] != e) continue;
+        for (int i4 = 0; i4 < pairs4 && j < cnt; ++i4) {
+            const int4 v = pk4[i4];
+            if (v.x != e && v.y != e && v.z != e && v.w != e) continue;
+            const int vs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+            if (vs[u] != e) continue;
+            const int i = i4 * 4 + u;
             const int p = base + (j >> 3);
             if (p < max_probs) {
                 const int row = i / slots, slot = i - row * slots;
@@ -180,6 +192,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R,
                 }
             }
             ++j;
+            }
         }
         for (; j & 7; ++j) {
             const int p = base + (j >> 3);
@@ -362,7 +375,7 @@ int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int ma
     if (max_probs < 1 || !pick || !prob_expert || !prob_count || !prob_rows || !pair_loc) return TF_EINVAL;
     if (world < 1 || rank < 0 || rank >= world || experts < 1 || experts > experts_total) return TF_EINVAL;
     if (world > 1 && (experts % world || !prob_sel || !sel_count)) return TF_EINVAL;
-    size_t smem = (size_t)rows * slots * sizeof(int);
+    size_t smem = (size_t)((rows * slots + 3) / 4) * 4 * sizeof(int);
     void* args[] = {&pick, &rows, &slots, &experts_total, &max_probs, &prob_expert, &prob_count, &prob_rows, &pair_loc,
                     &experts, &rank, &world, &prob_sel, &sel_count};
     return tf::launch_pdl((const void*)tf::moe_group_kernel, dim3(1), dim3(1024), smem, static_cast<cudaStream_t>(stream), args) ==
