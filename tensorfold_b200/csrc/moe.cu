@@ -137,66 +137,80 @@ __device__ int scan1024(int v, int* warp_tot, int& total) {
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* pick, int R, int slots, int NE, int max_probs, int* prob_expert,
                                                          int* prob_count, int* prob_rows, int* pair_loc, int E, int rank, int world,
                                                          int* prob_sel, int* sel_count) {
-    extern __shared__ __align__(16) int sh_pick[];   // R * slots picks, padded to a multiple of four
+    extern __shared__ int sh_pick[];             // R * slots picks
     __shared__ int warp_tot[33];
+    __shared__ int cnt_s[1024], base_s[1024], sel_s[1024];
     pdl_launch_dependents();
     pdl_wait();
-    const int e = threadIdx.x;
-    const int pairs = R * slots, pairs4 = (pairs + 3) >> 2;      // the picks are scanned four at a time (padded with -1)
-    for (int i = e; i < pairs4 * 4; i += 1024) sh_pick[i] = i < pairs ? pick[i] : -1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pairs = R * slots, chunks = (pairs + 31) >> 5;
+    for (int i = tid; i < pairs; i += 1024) sh_pick[i] = pick[i];
     __syncthreads();
-    const int4* pk4 = reinterpret_cast<const int4*>(sh_pick);
-    int cnt = 0;
-    if (e < NE) {
+    // members of each expert: a warp per expert (ids warp, warp + 32, ...), lanes over the pairs
+    for (int e = warp; e < NE; e += 32) {
+        int c = 0;
 #pragma unroll 4
-        for (int i = 0; i < pairs4; ++i) {
-            const int4 v = pk4[i];
-            cnt += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+        for (int k = 0; k < chunks; ++k) {
+            const int i = k * 32 + lane;
+            c += __popc(__ballot_sync(0xffffffffu, i < pairs && sh_pick[i] == e));
         }
+        if (lane == 0) cnt_s[e] = c;
     }
-    const int mine = (cnt + 7) >> 3;             // problems of this expert
+    __syncthreads();
+    const int cnt = tid < NE ? cnt_s[tid] : 0;
+    const int mine = (cnt + 7) >> 3;             // problems of expert `tid`
     int all;
     const int base = scan1024(mine, warp_tot, all);
     const int total = min(all, max_probs);
-    if (e == 0) prob_count[0] = total;
+    if (tid == 0) prob_count[0] = total;
     const int per = world > 1 ? E / world : 0;
-    const bool shared = e >= E;
-    // problems of this expert owned by this rank: all or none for a routed expert, every world-th for the shared one
+    // problems of an expert owned by this rank: all or none for a routed expert, every world-th for the shared one
     int owned = 0;
-    if (world > 1 && e < NE) owned = shared ? (mine + world - 1 - rank) / world : (e / per == rank ? mine : 0);
+    if (world > 1 && tid < NE) owned = tid >= E ? (mine + world - 1 - rank) / world : (tid / per == rank ? mine : 0);
     int all_owned = 0;
     const int sel_base = world > 1 ? scan1024(owned, warp_tot, all_owned) : 0;
-    if (world > 1 && e == 0) sel_count[0] = all_owned;      // owned problems never exceed max_probs: they are a subset
-    if (e < NE && cnt > 0) {
-        int j = 0, sel = sel_base;
-        for (int i4 = 0; i4 < pairs4 && j < cnt; ++i4) {
-            const int4 v = pk4[i4];
-            if (v.x != e && v.y != e && v.z != e && v.w != e) continue;
-            const int vs[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-            if (vs[u] != e) continue;
-            const int i = i4 * 4 + u;
-            const int p = base + (j >> 3);
-            if (p < max_probs) {
-                const int row = i / slots, slot = i - row * slots;
-                prob_rows[p * 8 + (j & 7)] = row * kMaxSlots + slot;
-                pair_loc[i] = p * 8 + (j & 7);
-                if ((j & 7) == 0) {
-                    if (world == 1) {
-                        prob_expert[p] = e;
-                    } else {
-                        prob_expert[p] = shared ? per : e % per;
-                        if (shared ? ((j >> 3) % world == rank) : (e / per == rank)) prob_sel[sel++] = p;
+    if (world > 1 && tid == 0) sel_count[0] = all_owned;    // owned problems never exceed max_probs: they are a subset
+    base_s[tid] = base;
+    sel_s[tid] = sel_base;
+    __syncthreads();
+    // placement, in row order: a member's place is the count of earlier members of its expert
+    for (int e = warp; e < NE; e += 32) {
+        if (cnt_s[e] == 0) continue;
+        const bool shared = e >= E;
+        const int b0 = base_s[e];
+        int j = 0;
+#pragma unroll 2
+        for (int k = 0; k < chunks; ++k) {
+            const int i = k * 32 + lane;
+            const bool hit = i < pairs && sh_pick[i] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int jj = j + __popc(m & ((1u << lane) - 1u));
+                const int pq = jj >> 3, p = b0 + pq;
+                if (p < max_probs) {
+                    const int row = i / slots, slot = i - row * slots;
+                    prob_rows[p * 8 + (jj & 7)] = row * kMaxSlots + slot;
+                    pair_loc[i] = p * 8 + (jj & 7);
+                    if ((jj & 7) == 0) {
+                        if (world == 1) {
+                            prob_expert[p] = e;
+                        } else {
+                            prob_expert[p] = shared ? per : e % per;
+                            if (shared) {
+                                if (pq % world == rank) prob_sel[sel_s[e] + pq / world] = p;
+                            } else if (e / per == rank) {
+                                prob_sel[sel_s[e] + pq] = p;
+                            }
+                        }
                     }
                 }
             }
-            ++j;
-            }
+            j += __popc(m);
         }
-        for (; j & 7; ++j) {
-            const int p = base + (j >> 3);
-            if (p < max_probs) prob_rows[p * 8 + (j & 7)] = -1;
+        const int pad = ((j + 7) & ~7) - j;      // absent members of the expert's last problem
+        if (lane < pad) {
+            const int jj = j + lane, p = b0 + (jj >> 3);
+            if (p < max_probs) prob_rows[p * 8 + (jj & 7)] = -1;
         }
     }
 }
@@ -375,7 +389,7 @@ int tf_moe_group(const int* pick, int rows, int slots, int experts_total, int ma
     if (max_probs < 1 || !pick || !prob_expert || !prob_count || !prob_rows || !pair_loc) return TF_EINVAL;
     if (world < 1 || rank < 0 || rank >= world || experts < 1 || experts > experts_total) return TF_EINVAL;
     if (world > 1 && (experts % world || !prob_sel || !sel_count)) return TF_EINVAL;
-    size_t smem = (size_t)((rows * slots + 3) / 4) * 4 * sizeof(int);
+    size_t smem = (size_t)rows * slots * sizeof(int);
     void* args[] = {&pick, &rows, &slots, &experts_total, &max_probs, &prob_expert, &prob_count, &prob_rows, &pair_loc,
                     &experts, &rank, &world, &prob_sel, &sel_count};
     return tf::launch_pdl((const void*)tf::moe_group_kernel, dim3(1), dim3(1024), smem, static_cast<cudaStream_t>(stream), args) ==
