@@ -73,16 +73,35 @@ __global__ void __launch_bounds__(kRowsPerCta * 4) gdn_kernel(const GdnArgs a) {
     for (int t0 = 0; t0 < n; t0 += kTile) {
         const int rows = min(kTile, n - t0);
         __syncthreads();
-        for (int e = tid; e < rows * kDk; e += kRowsPerCta * 4) {
-            const int r = e / kDk, d = e % kDk;
+        // 16-byte loads: 8 bf16 values of a key/query row, or of a row's 32 values, per thread
+        for (int e = tid; e < rows * (kDk / 8); e += kRowsPerCta * 4) {
+            const int r = e / (kDk / 8), d = (e % (kDk / 8)) * 8;
             const size_t at = ((size_t)(r0 + t0 + r) * a.KH + kh) * kDk + d;
-            ks[r][d] = bf2f(kp[at]);
-            if (OUT) qs[r][d] = bf2f(qp[at]);
+            float f[8];
+            unpack8(*reinterpret_cast<const uint4*>(kp + at), f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ks[r][d + i] = f[i];
+            if (OUT) {
+                unpack8(*reinterpret_cast<const uint4*>(qp + at), f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qs[r][d + i] = f[i];
+            }
         }
-        for (int e = tid; e < rows * kRowsPerCta; e += kRowsPerCta * 4) {
-            const int r = e / kRowsPerCta, c = e % kRowsPerCta;
-            const int dr = blockIdx.x * kRowsPerCta + c;
-            vs[r][c] = dr < a.DV ? bf2f(vp[((size_t)(r0 + t0 + r) * a.VH + head) * a.DV + dr]) : 0.f;
+        if ((a.DV & 7) == 0) {
+            for (int e = tid; e < rows * (kRowsPerCta / 8); e += kRowsPerCta * 4) {
+                const int r = e / (kRowsPerCta / 8), c = (e % (kRowsPerCta / 8)) * 8;
+                const int dr = blockIdx.x * kRowsPerCta + c;
+                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (dr < a.DV) unpack8(*reinterpret_cast<const uint4*>(vp + ((size_t)(r0 + t0 + r) * a.VH + head) * a.DV + dr), f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vs[r][c + i] = f[i];
+            }
+        } else {
+            for (int e = tid; e < rows * kRowsPerCta; e += kRowsPerCta * 4) {
+                const int r = e / kRowsPerCta, c = e % kRowsPerCta;
+                const int dr = blockIdx.x * kRowsPerCta + c;
+                vs[r][c] = dr < a.DV ? bf2f(vp[((size_t)(r0 + t0 + r) * a.VH + head) * a.DV + dr]) : 0.f;
+            }
         }
         if (tid < rows) {
             gs[tid] = gp[(size_t)(r0 + t0 + tid) * a.VH + head];
@@ -173,7 +192,7 @@ int tf_gdn_chain(const void* q, const void* k, const void* v, const float* g, co
                  void* stream) {
     if (tf::check(n_seqs, 1, k_heads, v_heads, dk, dv) != TF_OK) return TF_EINVAL;
     if (!q || !k || !v || !g || !beta || !state || !y || !seq_start) return TF_EINVAL;
-    if (((uintptr_t)state | (uintptr_t)state_out) & 15) return TF_EALIGN;
+    if (((uintptr_t)state | (uintptr_t)state_out | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) return TF_EALIGN;
     tf::GdnArgs a = {};
     a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
     a.v = static_cast<const __nv_bfloat16*>(v); a.g = g; a.beta = beta;
@@ -193,7 +212,7 @@ int tf_gdn_replay(const void* k, const void* v, const float* g, const float* bet
                   long long rec_g_stride, long long state_stride, int k_heads, int v_heads, int dk, int dv, void* stream) {
     if (tf::check(n_seqs, layers, k_heads, v_heads, dk, dv) != TF_OK) return TF_EINVAL;
     if (!k || !v || !g || !beta || !state || !seq_start || !keep) return TF_EINVAL;
-    if ((uintptr_t)state & 15 || state_stride % 4) return TF_EALIGN;
+    if ((uintptr_t)state & 15 || state_stride % 4 || (((uintptr_t)k | (uintptr_t)v) & 15) || rec_k_stride % 8 || rec_v_stride % 8) return TF_EALIGN;
     tf::GdnArgs a = {};
     a.q = nullptr; a.k = static_cast<const __nv_bfloat16*>(k);
     a.v = static_cast<const __nv_bfloat16*>(v); a.g = g; a.beta = beta;
