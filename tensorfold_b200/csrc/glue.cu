@@ -229,6 +229,16 @@ __global__ void gdn_pre_kernel(const __nv_bfloat16* qkv, size_t qkv_stride, cons
     const int seq = row_seq[row], idx = row_idx[row];      // idx: the row's place in its sequence's chain
     const int ch0 = head * 128 + lane * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // the 4 taps of this lane's 4 channels are 16 consecutive bf16 values: two 16-byte loads
+    float wt[16];
+    {
+        const uint4* wp = reinterpret_cast<const uint4*>(conv_w + (size_t)ch0 * 4);
+        float lo[8], hi[8];
+        unpack8(wp[0], lo);
+        unpack8(wp[1], hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { wt[i] = lo[i]; wt[8 + i] = hi[i]; }
+    }
     // taps 0..3 read rows idx-3..idx of [conv_state (3 rows); this sequence's window rows]
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -238,7 +248,7 @@ __global__ void gdn_pre_kernel(const __nv_bfloat16* qkv, size_t qkv_stride, cons
         const uint2 xv = *reinterpret_cast<const uint2*>(p);
         const float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] = __fmaf_rn(xf[i], bf2f(conv_w[(size_t)(ch0 + i) * 4 + j]), acc[i]);
+        for (int i = 0; i < 4; ++i) acc[i] = __fmaf_rn(xf[i], wt[i * 4 + j], acc[i]);
     }
     float c[4];
 #pragma unroll
@@ -363,6 +373,7 @@ int tf_gdn_pre(const void* qkv, size_t qkv_stride, const void* conv_state, const
     if (!qkv || !conv_state || !conv_w || !row_seq || !row_idx || !a || !b || !a_log || !dt_bias) return TF_EINVAL;
     if (!q_out || !k_out || !v_out || !g_out || !beta_out || qkv_stride % 4) return TF_EINVAL;
     if (((uintptr_t)qkv | (uintptr_t)conv_state | (uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out) & 7) return TF_EALIGN;
+    if ((uintptr_t)conv_w & 15) return TF_EALIGN;
     const int warps = 4, total = 2 * k_heads + v_heads;
     void* args[] = {&qkv, &qkv_stride, &conv_state, &conv_w, &row_seq, &row_idx, &a, &b, &ab_stride, &a_log, &dt_bias,
                     &q_out, &k_out, &v_out, &g_out, &beta_out, &k_heads, &v_heads};
