@@ -184,8 +184,11 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qg, size_t qg_stride, cons
     const int per = D >> 5;                                // values per lane
     if (head >= H + HK) {                                  // value rows: plain copy into the contiguous record
         const int hv = head - H - HK;
-        for (int i = 0; i < per; ++i)
-            v_out[((size_t)row * HK + hv) * D + lane * per + i] = vin[(size_t)row * v_stride + (size_t)hv * D + lane * per + i];
+        const __nv_bfloat16* vs = vin + (size_t)row * v_stride + (size_t)hv * D + lane * per;
+        __nv_bfloat16* vd = v_out + ((size_t)row * HK + hv) * D + lane * per;
+        if (per == 8) *reinterpret_cast<uint4*>(vd) = *reinterpret_cast<const uint4*>(vs);      // head_dim 256: one 16-byte copy
+        else if (per == 4) *reinterpret_cast<uint2*>(vd) = *reinterpret_cast<const uint2*>(vs);
+        else for (int i = 0; i < per; ++i) vd[i] = vs[i];
         return;
     }
     const bool is_q = head < H;
@@ -195,7 +198,9 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qg, size_t qg_stride, cons
     float* xn = xn_s + wib * D;
     float v[8];
     float ss = 0.f;
-    for (int i = 0; i < per; ++i) { v[i] = bf2f(src[lane * per + i]); ss += v[i] * v[i]; }
+    if (per == 8) unpack8(*reinterpret_cast<const uint4*>(src + lane * 8), v);                    // same values, one 16-byte load
+    else for (int i = 0; i < per; ++i) v[i] = bf2f(src[lane * per + i]);
+    for (int i = 0; i < per; ++i) ss += v[i] * v[i];
     const float inv = inv_rms(warp_sum(ss), D, eps);
     for (int i = 0; i < per; ++i) xn[lane * per + i] = round_bf16(v[i] * inv * bf2f(wn[lane * per + i]));
     __syncwarp();
@@ -358,6 +363,7 @@ int tf_attn_prep(const void* qg, size_t qg_stride, const void* k, size_t k_strid
     if (M < 1 || heads < 1 || kv_heads < 1 || (head_dim != 128 && head_dim != 256)) return TF_EINVAL;
     if (rope_half < 0 || 2 * rope_half > head_dim) return TF_EINVAL;
     if (!qg || !k || !v || !q_norm || !k_norm || !row_pos || !inv_freq || !q_out || !k_out || !v_out) return TF_EINVAL;
+    if ((((uintptr_t)qg | (uintptr_t)k | (uintptr_t)v | (uintptr_t)v_out) & 15) || (qg_stride | k_stride | v_stride) % 8) return TF_EALIGN;
     const int warps = 4, total = heads + 2 * kv_heads;
     void* args[] = {&qg, &qg_stride, &k, &k_stride, &v, &v_stride, &q_norm, &k_norm, &row_pos, &inv_freq, &rope_half,
                     &q_out, &k_out, &v_out, &heads, &kv_heads, &head_dim, &eps};
