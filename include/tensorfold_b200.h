@@ -55,15 +55,22 @@ int tf_qmm_workers(void);
  *          kernels below write it directly.
  * w_tiled: weights in this library's tile layout (tf_qmm_tiled_bytes / tf_qmm_tile below).
  * y  [M, N] bf16 (fp32 with TF_QMM_F32_OUT).  group is 64 or 32.  K a multiple of 64.
- * scratch: tf_qmm_scratch_bytes() bytes, 256-byte aligned; its first TF_QMM_COUNTER_BYTES bytes
- *          must be zero before the first call and are left zero by every call (the rest needs no
- *          initialisation). Calls that overlap on the GPU must not share scratch.
+ * scratch: tf_qmm_scratch_bytes() bytes, 256-byte aligned, all zero before the first call; afterwards
+ *          it belongs to the library (it holds parked K segments, their ready tags and a launch number
+ *          per worker that every call advances). Calls that overlap on the GPU must not share scratch;
+ *          calls on one stream, programmatic dependent launches included, may.
  */
 #define TF_QMM_COUNTER_BYTES 16384
 size_t tf_qmm_scratch_bytes(void);
 size_t tf_packed_bytes(int M, int K, int group);
 int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
            int K, int group, int flags, int* status, void* stream);
+
+/* Profiling aid, no counterpart in the reference: with `stamps` not NULL (device memory, 148 * 8 uint64)
+ * every later tf_qmm / tf_qmm_grouped launch on the current device writes eight %globaltimer values per
+ * worker CTA (kernel entry, first weight copy issued, predecessor's memory visible, first stage ready,
+ * main loop done, last segment parked, ordered sum done, last copy issued); NULL switches it off. */
+int tf_qmm_set_trace(void* stamps);
 
 /* Grouped form for mixture-of-experts layers: up to max_probs independent problems of 8 rows each in
  * one launch. Problem p multiplies its packed rows (x_packed + p * tf_packed_bytes(8, K, group)) with

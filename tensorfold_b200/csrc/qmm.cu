@@ -28,8 +28,11 @@
 // over all banks), then the tile's group sums as [groups in tile][Mp] fp32. A stage's activations
 // are again one contiguous range.
 //
-// Warp roles in a CTA: 16 consumer warps (one 16-column tile each), one producer thread (bulk
-// copies), one finisher warp that sums parked K segments so the consumers never wait on a fence.
+// Warp roles in a CTA: consumer warps (each one or two 16-column tiles of the block) and one producer
+// thread (bulk copies).
+//
+// What bounds the loop once the bytes arrive is the integer pipe (16 lanes a cycle per sub-partition):
+// a 16 x 64 record costs 12 shifts + 16 and-or operations there, so each of the 16 is one lop3.
 
 #include "common.cuh"
 
@@ -39,7 +42,7 @@ namespace {
 constexpr int kWorkers = 148;
 constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every row bucket, so that the
                                 // K segments (hence the bits) do not depend on the row count
-constexpr int kWarps = 16;      // consumer warps = column tiles per column block (baked into the layout)
+constexpr int kWarps = 16;      // column tiles per column block (baked into the layout)
 constexpr int kCols = kWarps * 16;
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 512 + (64 / group) * 64; }
@@ -49,8 +52,11 @@ __host__ __device__ constexpr int nibble_quad(int j) { return ((j >> 1) & 1) * 2
 // input (0..63) of a k tile that lane t feeds to k-step s at quad position `quad`
 __host__ __device__ constexpr int tile_k(int t, int s, int quad) { return 32 * (s >> 1) + 8 * t + 4 * (s & 1) + quad; }
 
-template <int G, int MB, int KTS, int STAGES>
+// One instantiation per row bucket: MB blocks of 8 rows, KTS k tiles a pipeline stage, T column tiles per
+// consumer warp (they share the activation loads), CTAS CTAs of the kernel that fit one SM.
+template <int G_, int MB_, int KTS_, int T_, int CTAS_>
 struct Cfg {
+    static constexpr int G = G_, MB = MB_, KTS = KTS_, T = T_, CTAS = CTAS_;
     static constexpr int REC = rec_bytes(G);
     static constexpr int GPT = 64 / G;                 // groups per k tile
     static constexpr int ROWS = MB * 8;                // = tf_padded_rows(M) for every M of the bucket
@@ -58,15 +64,38 @@ struct Cfg {
     static constexpr int W_BYTES = kWarps * KTS * REC;
     static constexpr int X_BYTES = KTS * XTILE;
     static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + 127) / 128) * 128;
-    static constexpr int THREADS = (kWarps + 2) * 32;   // consumers + producer warp + finisher warp
+    static constexpr int CW = kWarps / T;               // consumer warps
+    static constexpr int THREADS = (CW + 1) * 32;       // consumers + producer warp
+    // the ring takes the SM's shared memory (1 KB a CTA belongs to the system), split between CTAS CTAs
+    static constexpr int BUDGET = (CTAS == 2 ? 113 : 226) * 1024 - 512;
+    static constexpr int STAGES = BUDGET / (STAGE_BYTES + 16) > 12 ? 12 : BUDGET / (STAGE_BYTES + 16);
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
+    static_assert(STAGES >= 2, "the ring needs at least two stages");
+    static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
 };
+
+// Optional per-CTA timeline for profiling: when set (tf_qmm_set_trace), each launch writes eight
+// globaltimer stamps per CTA: 0 kernel entry, 1 first weight copy issued, 2 predecessor's memory visible
+// (griddepcontrol.wait passed), 3 consumers past their first full barrier, 4 main loop done, 5 last
+// segment parked or written, 6 ordered sum done, 7 producer's last copy issued.
+__device__ unsigned long long* g_trace = nullptr;
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr int kTraceLaunches = 32, kTraceSlots = 16;
+// layout: [148] per-CTA launch counters, then [launch % 32][cta][16] stamps
+__device__ __forceinline__ void stamp(unsigned long long* tr, int slot) {
+    if (tr != nullptr) tr[blockIdx.x * kTraceSlots + slot] = now_ns();
+}
 
 struct Args {
     const uint8_t* xp;
     const uint8_t* w;
     void* y;
-    int* counters;
+    uint32_t* epochs;
+    uint32_t* tags;
     float* slots;
     int* status;
     int M, N, K;
@@ -84,98 +113,47 @@ struct Args {
 };
 
 // Work items (column block, group of kItemTiles k tiles) are split evenly over kWorkers CTAs.
-__host__ __device__ inline int range_begin(int cta, int total) { return (int)((long long)cta * total / kWorkers); }
-__host__ __device__ inline int owner_of(int w, int total) { return (int)((((long long)w + 1) * kWorkers - 1) / total); }
+// cta * total stays below 2^31: the entry points refuse shapes with more than 2^30 / kWorkers items
+__host__ __device__ inline int range_begin(int cta, int total) { return (int)((unsigned)cta * (unsigned)total / (unsigned)kWorkers); }
 
 constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
+constexpr int kMaxThreads = 512;          // consumer threads of the widest configuration
+// scratch: [ticket words of the prefill kernel][parked segments, two slots a worker (this kernel uses one)]
+//          [launch numbers, one a worker][ready tags, one per worker and consumer thread]
+constexpr size_t kEpochOffset = TF_QMM_COUNTER_BYTES + 2 * kWorkers * kSlotFloats * sizeof(float);
+constexpr size_t kTagOffset = kEpochOffset + 1024;
+constexpr size_t kScratchBytes = kTagOffset + (size_t)kWorkers * kMaxThreads * sizeof(uint32_t);
 
-// A parked K segment of column block `cb` is complete in global memory: take a ticket; the last of
-// the block's segments to arrive adds them all in k order and writes the output. Run by NT threads:
-// the finisher warp (NT = 32) for a segment at the start of a CTA's range, while the consumers go on,
-// or all consumer warps together for the segment that ends the range, when they have nothing left
-// to do and the sum is on the kernel's critical path.
-template <int NT>
-__device__ __forceinline__ void group_sync() {
-    if (NT == 32) __syncwarp();
-    else named_bar_sync(1, NT);
+__device__ __forceinline__ void st_release(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
-template <int NT, bool MULTI>
-__device__ void finish_segment(const Args& a, int gb, int CB, int SPB, int total, int tid, int* list) {
-    __threadfence();
-    group_sync<NT>();
-    const int cb_begin = gb * SPB;
-    const int q = MULTI ? gb / CB : 0, cb = gb - q * CB;
-    const int prob = (MULTI && a.prob_sel) ? a.prob_sel[q] : q;
-    if (tid == 0) {
-        const int first = owner_of(cb_begin, total), last = owner_of(cb_begin + SPB - 1, total);
-        int nseg = 0;
-        for (int o = first; o <= last; ++o) {
-            const int ob = range_begin(o, total);
-            if (ob == range_begin(o + 1, total)) continue;       // a worker without work
-            list[nseg++] = 2 * o + (ob < cb_begin ? 1 : 0);      // its slot, in k order
-        }
-        list[kWorkers] = nseg;
-        list[kWorkers + 1] = atomicAdd(a.counters + gb, 1);
-    }
-    group_sync<NT>();
-    const int nseg = list[kWorkers];
-    if (list[kWorkers + 1] != nseg - 1) return;
-    __threadfence();
-    const int ncol4 = (min(kCols, a.N - cb * kCols) + 3) >> 2;
-    const int n4 = a.M * (kCols / 4);
-    constexpr int U = 4;          // elements in flight per thread and segment
-    for (int base = tid; base < n4; base += NT * U) {
-        float4 sum[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < nseg; j += 2) {
-            float4 v[2][U];
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj)
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int idx = base + NT * u;
-                    v[jj][u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (j + jj < nseg && idx < n4)
-                        v[jj][u] = __ldcg(reinterpret_cast<const float4*>(a.slots + (size_t)list[j + jj] * kSlotFloats) + idx);
-                }
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj)
-                if (j + jj < nseg) {
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        if (j + jj == 0) sum[u] = v[jj][u];
-                        else { sum[u].x += v[jj][u].x; sum[u].y += v[jj][u].y; sum[u].z += v[jj][u].z; sum[u].w += v[jj][u].w; }
-                    }
-                }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = base + NT * u;
-            if (idx >= n4) continue;
-            const int row = idx / (kCols / 4), c4 = idx - row * (kCols / 4);
-            if (c4 >= ncol4) continue;
-            const float e[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
-            const int col = cb * kCols + c4 * 4;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (col + i >= a.N) break;
-                const size_t at = (size_t)prob * a.y_stride + (size_t)row * a.N + col + i;
-                if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = e[i];
-                else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(e[i]);
-            }
-        }
-    }
-    if (tid == 0) a.counters[gb] = 0;      // leave the counters zero for the next call (every reader is past its ticket)
-}
-
-template <int G, int MB, int KTS, int STAGES, bool MULTI>
-__global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a) {
-    using C = Cfg<G, MB, KTS, STAGES>;
-    static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
+// How a column block cut along K is put together. The work items of a block are consecutive, so its
+// segments belong to consecutive workers: the first segment (the block's first k items) ends one
+// worker's range, every later segment starts the next worker's range. A worker therefore "parks" at
+// most one segment, the first of its range, early in the kernel: each consumer thread stores its
+// accumulators (its own float4s, thread-major, so the stores coalesce) and then a tag carrying the
+// launch number with release order. The worker that holds the block's FIRST segment is the one that
+// finishes the block: at the end of its range it keeps that segment in registers, waits (bounded) for
+// the tags of the later segments, which were parked long before unless their worker started late, adds
+// them in worker order, which is k order, and writes the output. No tickets, no fences on the critical
+// path, and nothing to reset. The launch number is the worker's own counter in scratch, advanced once
+// per launch before dependents may start, so every worker of a launch holds the same number.
+template <class C, bool MULTI>
+__global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) {
+    constexpr int MB = C::MB, KTS = C::KTS, STAGES = C::STAGES, CW = C::CW, T = C::T, NC = CW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ int seg_list[2][kWorkers + 2];   // [0] finisher warp, [1] consumers
+    __shared__ uint32_t epoch_s;
+    // every thread derives the same per-launch trace base: the CTA's launch counter is bumped by thread 0
+    // only after all threads have read it (the barrier below)
+    unsigned long long* tr = g_trace;
+    if (tr != nullptr) tr += kWorkers + (tr[blockIdx.x] % kTraceLaunches) * (kWorkers * kTraceSlots);
+    if (threadIdx.x == 0) stamp(tr, 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K >> 6;                              // k tiles
     const int CB = (a.N + kCols - 1) / kCols;             // column blocks
@@ -197,37 +175,35 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), kWarps);
+            mbar_init(empty_bar(s), CW);
         }
         mbar_fence_init();
+        epoch_s = atomicAdd(a.epochs + blockIdx.x, 1u) + 1u;   // this launch's number: the same on every worker
+        if (g_trace != nullptr) g_trace[blockIdx.x] += 1;
     }
     __syncthreads();
     pdl_launch_dependents();     // the next kernel may be scheduled; it still waits for this one's memory
 
-    // the first and the last segment of this CTA's range may be parts of a column block
-    const int cb_first = begin < end ? begin / SPB : 0, cb_last = begin < end ? (end - 1) / SPB : 0;
-    // a partial segment that ends the range is summed by the consumers themselves; one that starts a
-    // longer range goes to the finisher warp
-    const bool part_first = cb_last != cb_first && begin > cb_first * SPB;
-
-    if (warp == kWarps) {
+    if (warp == CW) {
         // ------------------------------- producer: one thread ----------------------------------
         // Weights never change during a forward, so the first ring of weight copies is issued before
         // waiting for the previous kernel; the activations (its output) follow after the wait.
         if (lane == 0 && begin < end) {
             int s = 0, issued = 0;
             uint32_t phase = 1;
-            int gb = cb_first, st = begin - gb * SPB;
-            int prob = MULTI ? gb / CB : 0, cb = gb - prob * CB;
             auto picked = [&](int q) { return (MULTI && a.prob_sel) ? a.prob_sel[q] : q; };
-            const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[picked(prob)] * a.w_stride : 0);
-            const uint8_t* xbase = a.xp + (size_t)picked(prob) * a.xp_stride;
             int early_kt0[STAGES], early_nkt[STAGES];
             bool waited = multi;
-            for (int it = begin; it < end; ++it) {
-                for (int sub = 0; sub < item_tiles; sub += KTS) {
-                    const int kt0 = st * item_tiles + sub, nkt = min(KTS, KT - kt0);
-                    if (nkt <= 0) break;
+            int it = begin;
+            while (it < end) {
+                const int gb = it / SPB, pq = MULTI ? gb / CB : 0, cb = gb - pq * CB;
+                const int cb_begin = gb * SPB, seg_end = min(cb_begin + SPB, end);
+                const uint8_t* wbase = a.w + (multi ? (size_t)a.prob_expert[picked(pq)] * a.w_stride : 0) +
+                                       (size_t)cb * KT * (kWarps * C::REC);
+                const uint8_t* xbase = a.xp + (multi ? (size_t)picked(pq) * a.xp_stride : 0);
+                const int kt_end = min(KT, (seg_end - cb_begin) * item_tiles);
+                for (int kt0 = (it - cb_begin) * item_tiles; kt0 < kt_end; kt0 += KTS) {
+                    const int nkt = min(KTS, kt_end - kt0);
                     if (issued == STAGES && !waited) {
                         pdl_wait();
                         for (int e = 0; e < STAGES; ++e)
@@ -239,25 +215,16 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     uint8_t* sb = stage0 + s * C::STAGE_BYTES;
                     const uint32_t wbytes = (uint32_t)(nkt * kWarps * C::REC), xbytes = (uint32_t)(nkt * C::XTILE);
                     mbar_arrive_expect_tx(full_bar(s), wbytes + xbytes);
-                    bulk_g2s(smem_u32(sb), wbase + ((size_t)cb * KT + kt0) * (kWarps * C::REC), wbytes, full_bar(s));
+                    bulk_g2s(smem_u32(sb), wbase + (size_t)kt0 * (kWarps * C::REC), wbytes, full_bar(s));
+                    if (issued == 0) stamp(tr, 1);
                     if (waited) bulk_g2s(smem_u32(sb + C::W_BYTES), xbase + (size_t)kt0 * C::XTILE, xbytes, full_bar(s));
                     else { early_kt0[issued] = kt0; early_nkt[issued] = nkt; }
                     ++issued;
                     if (++s == STAGES) { s = 0; phase ^= 1; }
                 }
-                if (++st == SPB) {
-                    st = 0;
-                    ++gb;
-                    if (++cb == CB) {
-                        cb = 0;
-                        ++prob;
-                        if (multi && it + 1 < end) {
-                            wbase = a.w + (size_t)a.prob_expert[picked(prob)] * a.w_stride;
-                            xbase = a.xp + (size_t)picked(prob) * a.xp_stride;
-                        }
-                    }
-                }
+                it = seg_end;
             }
+            stamp(tr, 7);
             if (!waited) {
                 pdl_wait();
                 for (int e = 0; e < issued; ++e)
@@ -268,20 +235,17 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
         return;
     }
     pdl_wait();                  // everything below reads or writes what other kernels produce or read
+    if (threadIdx.x == 0) stamp(tr, 2);
     if (begin >= end) return;
-    if (warp == kWarps + 1) {
-        // ------------------- finisher: sums parked segments while the consumers go on -----------
-        if (part_first) {
-            named_bar_sync(2, (kWarps + 1) * 32);
-            finish_segment<32, MULTI>(a, cb_first, CB, SPB, total, lane, seg_list[0]);
-        }
-        return;
-    }
 
     // ----------------------------------- consumer warps ---------------------------------------
     const int g = lane >> 2, t = lane & 3;
     const int xlane = g * 128 + ((t * 16) ^ ((g & 1) << 6));   // this lane's B-operand bytes inside a row block
-    float acc[MB][4];
+    // opaque to the compiler on purpose: as registers they let (w >> s) & mask | magic be one lop3
+    uint32_t nib_mask = 0x000F000Fu, magic = 0x43004300u;
+    asm volatile("" : "+r"(nib_mask), "+r"(magic));
+    const uint32_t epoch = epoch_s;
+    float acc[T][MB][4];
     int s = 0;
     uint32_t phase = 0;
     int it = begin;
@@ -291,36 +255,41 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
         const int cb_begin = gb * SPB, cb_end = cb_begin + SPB;
         const int seg_begin = it, seg_end = cb_end < end ? cb_end : end;
 #pragma unroll
-        for (int rb = 0; rb < MB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
+        for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+            for (int rb = 0; rb < MB; ++rb) acc[ti][rb][0] = acc[ti][rb][1] = acc[ti][rb][2] = acc[ti][rb][3] = 0.f;
 
-        for (; it < seg_end; ++it)
-        for (int sub = 0; sub < item_tiles; sub += KTS) {
-            const int nkt = min(KTS, KT - ((it - cb_begin) * item_tiles + sub));
-            if (nkt <= 0) break;
+        const int kt_end = min(KT, (seg_end - cb_begin) * item_tiles);
+        for (int kt0 = (it - cb_begin) * item_tiles; kt0 < kt_end; kt0 += KTS) {
+            const int nkt = min(KTS, kt_end - kt0);
             mbar_wait(full_bar(s), phase, a.status);
+            if (tr != nullptr && threadIdx.x == 0 && it == begin && kt0 == (it - cb_begin) * item_tiles) stamp(tr, 3);
             const uint8_t* sb = stage0 + s * C::STAGE_BYTES;
-            const uint8_t* wrec = sb + warp * C::REC;
+            const uint8_t* wrec = sb + warp * T * C::REC;
             const uint8_t* xst = sb + C::W_BYTES;
 #pragma unroll
             for (int kt = 0; kt < KTS; ++kt) {
                 if (kt < nkt) {
-                    const uint8_t* rec = wrec + kt * (kWarps * C::REC);
-                    const uint4 wq = *reinterpret_cast<const uint4*>(rec + lane * 16);
-                    const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
-                    uint32_t af[4][4];
-#pragma unroll
-                    for (int s4 = 0; s4 < 4; ++s4)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) af[s4][i] = ((wv[s4] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
-                    float sc[C::GPT][2], bi[C::GPT][2];
-#pragma unroll
-                    for (int h = 0; h < C::GPT; ++h) {
-                        const uint2 p = *reinterpret_cast<const uint2*>(rec + 512 + h * 64 + g * 8);
-                        sc[h][0] = bf16_lo(p.x); bi[h][0] = bf16_hi(p.x);
-                        sc[h][1] = bf16_lo(p.y); bi[h][1] = bf16_hi(p.y);
-                    }
                     const uint8_t* xt = xst + kt * C::XTILE;
                     const float* xsums = reinterpret_cast<const float*>(xt + C::ROWS * 128) + 2 * t;
+                    uint32_t af[T][4][4];
+                    float sc[T][C::GPT][2], bi[T][C::GPT][2];
+#pragma unroll
+                    for (int ti = 0; ti < T; ++ti) {
+                        const uint8_t* rec = wrec + kt * (kWarps * C::REC) + ti * C::REC;
+                        const uint4 wq = *reinterpret_cast<const uint4*>(rec + lane * 16);
+                        const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                        for (int s4 = 0; s4 < 4; ++s4)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) af[ti][s4][i] = and_or(i ? wv[s4] >> (4 * i) : wv[s4], nib_mask, magic);
+#pragma unroll
+                        for (int h = 0; h < C::GPT; ++h) {
+                            const uint2 p = *reinterpret_cast<const uint2*>(rec + 512 + h * 64 + g * 8);
+                            sc[ti][h][0] = bf16_lo(p.x); bi[ti][h][0] = bf16_hi(p.x);
+                            sc[ti][h][1] = bf16_lo(p.y); bi[ti][h][1] = bf16_hi(p.y);
+                        }
+                    }
 #pragma unroll
                     for (int rb = 0; rb < MB; ++rb) {
                         const uint4 x0 = *reinterpret_cast<const uint4*>(xt + rb * 1024 + xlane);
@@ -330,14 +299,19 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
 #pragma unroll
                         for (int h = 0; h < C::GPT; ++h) {
                             const float2 xs = *reinterpret_cast<const float2*>(xsums + h * C::ROWS + rb * 8);
-                            float p[4] = {-128.f * xs.x, -128.f * xs.y, -128.f * xs.x, -128.f * xs.y};
+                            const float i0 = -128.f * xs.x, i1 = -128.f * xs.y;
 #pragma unroll
-                            for (int s4 = h * SPG; s4 < (h + 1) * SPG; ++s4)
-                                mma_bf16_16816(p, af[s4], xb[2 * s4], xb[2 * s4 + 1], p);
-                            acc[rb][0] = __fmaf_rn(bi[h][0], xs.x, __fmaf_rn(sc[h][0], p[0], acc[rb][0]));
-                            acc[rb][1] = __fmaf_rn(bi[h][0], xs.y, __fmaf_rn(sc[h][0], p[1], acc[rb][1]));
-                            acc[rb][2] = __fmaf_rn(bi[h][1], xs.x, __fmaf_rn(sc[h][1], p[2], acc[rb][2]));
-                            acc[rb][3] = __fmaf_rn(bi[h][1], xs.y, __fmaf_rn(sc[h][1], p[3], acc[rb][3]));
+                            for (int ti = 0; ti < T; ++ti) {
+                                float p[4] = {i0, i1, i0, i1};
+#pragma unroll
+                                for (int s4 = h * SPG; s4 < (h + 1) * SPG; ++s4)
+                                    mma_bf16_16816(p, af[ti][s4], xb[2 * s4], xb[2 * s4 + 1], p);
+                                float* ac = acc[ti][rb];
+                                ac[0] = __fmaf_rn(bi[ti][h][0], xs.x, __fmaf_rn(sc[ti][h][0], p[0], ac[0]));
+                                ac[1] = __fmaf_rn(bi[ti][h][0], xs.y, __fmaf_rn(sc[ti][h][0], p[1], ac[1]));
+                                ac[2] = __fmaf_rn(bi[ti][h][1], xs.x, __fmaf_rn(sc[ti][h][1], p[2], ac[2]));
+                                ac[3] = __fmaf_rn(bi[ti][h][1], xs.y, __fmaf_rn(sc[ti][h][1], p[3], ac[3]));
+                            }
                         }
                     }
                 }
@@ -346,11 +320,54 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
             if (lane == 0) mbar_arrive(empty_bar(s));
             if (++s == STAGES) { s = 0; phase ^= 1; }
         }
+        it = seg_end;
 
-        // ---- segment done: whole column block -> write; part of one -> park it for the finisher ----
-        const bool whole = (seg_begin == cb_begin) && (seg_end == cb_end);
-        const int col0 = cb * kCols + warp * 16 + g;
-        if (whole) {
+        // ---- segment done ----
+        if (tr != nullptr && threadIdx.x == 0 && seg_end == end) stamp(tr, 4);
+        if (seg_begin > cb_begin) {
+            // a later segment of a block some earlier worker finishes: park it (always the first of this range)
+            float4* slot = reinterpret_cast<float4*>(a.slots + (size_t)blockIdx.x * kSlotFloats);
+#pragma unroll
+            for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+                for (int rb = 0; rb < MB; ++rb)
+                    __stcg(slot + (ti * MB + rb) * NC + threadIdx.x,
+                           make_float4(acc[ti][rb][0], acc[ti][rb][1], acc[ti][rb][2], acc[ti][rb][3]));
+            st_release(a.tags + (size_t)blockIdx.x * kMaxThreads + threadIdx.x, epoch);
+            if (tr != nullptr && threadIdx.x == 0) stamp(tr, 5);
+            continue;
+        }
+        if (seg_end < cb_end) {
+            // the block's first segment: add the later ones, parked by the next workers, in worker order
+            for (int o = blockIdx.x + 1; o < kWorkers; ++o) {
+                const int ob = range_begin(o, total);
+                if (ob >= cb_end) break;
+                if (range_begin(o + 1, total) == ob) continue;       // a worker without work
+                const uint32_t* tag = a.tags + (size_t)o * kMaxThreads + threadIdx.x;
+                bool ready = false;
+                for (int spin = 0; spin < (1 << 20); ++spin)
+                    if (ld_acquire(tag) == epoch) { ready = true; break; }
+                if (!ready) report(a.status, TF_ESTALL);
+                const float4* slot = reinterpret_cast<const float4*>(a.slots + (size_t)o * kSlotFloats);
+                float4 v[T][MB];
+#pragma unroll
+                for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+                    for (int rb = 0; rb < MB; ++rb) v[ti][rb] = __ldcg(slot + (ti * MB + rb) * NC + threadIdx.x);
+#pragma unroll
+                for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+                    for (int rb = 0; rb < MB; ++rb) {
+                        acc[ti][rb][0] += v[ti][rb].x; acc[ti][rb][1] += v[ti][rb].y;
+                        acc[ti][rb][2] += v[ti][rb].z; acc[ti][rb][3] += v[ti][rb].w;
+                    }
+            }
+            if (tr != nullptr && threadIdx.x == 0) stamp(tr, 6);
+        }
+        // a whole block, or a finished one: write the output
+#pragma unroll
+        for (int ti = 0; ti < T; ++ti) {
+            const int col0 = cb * kCols + (warp * T + ti) * 16 + g;
 #pragma unroll
             for (int rb = 0; rb < MB; ++rb)
 #pragma unroll
@@ -358,37 +375,27 @@ __global__ void __launch_bounds__((kWarps + 2) * 32, 1) qmm_kernel(const Args a)
                     const int row = rb * 8 + 2 * t + (i & 1), col = col0 + (i >> 1) * 8;
                     if (row < a.M && col < a.N) {
                         const size_t at = (size_t)prob * a.y_stride + (size_t)row * a.N + col;
-                        if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = acc[rb][i];
-                        else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(acc[rb][i]);
+                        if (a.f32_out) reinterpret_cast<float*>(a.y)[at] = acc[ti][rb][i];
+                        else reinterpret_cast<__nv_bfloat16*>(a.y)[at] = f2bf(acc[ti][rb][i]);
                     }
                 }
-        } else {
-            // slot 2*cta + 1 when this CTA entered the column block from an earlier one, else 2*cta
-            const int later = begin < cb_begin ? 1 : 0;
-            float* slot = a.slots + (size_t)(2 * blockIdx.x + later) * kSlotFloats;
-#pragma unroll
-            for (int rb = 0; rb < MB; ++rb)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = rb * 8 + 2 * t + (i & 1);
-                    if (row < a.M) __stcg(slot + row * kCols + warp * 16 + g + (i >> 1) * 8, acc[rb][i]);
-                }
-            if (seg_end == end) finish_segment<kWarps * 32, MULTI>(a, gb, CB, SPB, total, threadIdx.x, seg_list[1]);
-            else asm volatile("bar.arrive 2, %0;" ::"r"((kWarps + 1) * 32) : "memory");   // the finisher takes it; go on
         }
     }
+    if (threadIdx.x == 0) stamp(tr, 9);
 }
 
-template <int G, int MB, int KTS, int STAGES, bool MULTI = false>
+template <class C, bool MULTI = false>
 int launch(const Args& a, cudaStream_t stream) {
-    using C = Cfg<G, MB, KTS, STAGES>;
-    static_assert(C::SMEM <= 227 * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<G, MB, KTS, STAGES, MULTI>;
-    static bool configured = false;   // per instantiation; the attribute is per function and idempotent
-    if (!configured) {
+    static_assert(C::SMEM <= (C::CTAS == 2 ? 113 : 227) * 1024, "stage ring does not fit shared memory");
+    auto kern = qmm_kernel<C, MULTI>;
+    // the opt-in is per device: keep one flag per device ordinal
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return TF_ECUDA; }
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
             return TF_ECUDA;
-        configured = true;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kWorkers);
@@ -404,21 +411,27 @@ int launch(const Args& a, cudaStream_t stream) {
     return TF_OK;
 }
 
-template <int G, int MB, int KTS>
-constexpr int stages_for() {
-    constexpr int budget = 224 * 1024;
-    constexpr int stage = ((kWarps * KTS * rec_bytes(G) + KTS * MB * 8 * (128 + 4 * (64 / G)) + 127) / 128) * 128 + 16;
-    return budget / stage > 8 ? 8 : budget / stage;
+inline int variant() {
+    static const int v = [] { const char* e = std::getenv("TF_QMM_VARIANT"); return e ? atoi(e) : 0; }();
+    return v;
 }
 
 template <int G>
 int dispatch(const Args& a, cudaStream_t stream) {
-    // one CTA per SM; the stage ring takes nearly all of shared memory (about 30 MB in flight chip-wide)
-    if (a.M <= 8) return launch<G, 1, 4, stages_for<G, 1, 4>()>(a, stream);
-    if (a.M <= 16) return launch<G, 2, 4, stages_for<G, 2, 4>()>(a, stream);
-    if (a.M <= 32) return launch<G, 4, 4, stages_for<G, 4, 4>()>(a, stream);
-    if (a.M <= 64) return launch<G, 8, 2, stages_for<G, 8, 2>()>(a, stream);
-    return launch<G, 16, 2, stages_for<G, 16, 2>()>(a, stream);
+    if (a.M <= 8) {
+        switch (variant()) {
+            case 1: return launch<Cfg<G, 1, 4, 2, 1>>(a, stream);
+            case 2: return launch<Cfg<G, 1, 2, 2, 2>>(a, stream);
+            case 3: return launch<Cfg<G, 1, 2, 1, 1>>(a, stream);
+            case 4: return launch<Cfg<G, 1, 2, 2, 1>>(a, stream);
+            case 5: return launch<Cfg<G, 1, 2, 1, 2>>(a, stream);
+            default: return launch<Cfg<G, 1, 4, 1, 1>>(a, stream);
+        }
+    }
+    if (a.M <= 16) return launch<Cfg<G, 2, 4, 1, 1>>(a, stream);
+    if (a.M <= 32) return launch<Cfg<G, 4, 4, 1, 1>>(a, stream);
+    if (a.M <= 64) return launch<Cfg<G, 8, 2, 1, 1>>(a, stream);
+    return launch<Cfg<G, 16, 2, 1, 1>>(a, stream);
 }
 
 // ---- relayout kernels: one thread per output word / pair -----------------------------------------
@@ -508,7 +521,12 @@ __global__ void pack_rows_kernel(const __nv_bfloat16* x, uint8_t* xp, float* xs_
 
 extern "C" {
 
-int tf_version(void) { return 1000; }
+int tf_version(void) { return 1001; }
+
+int tf_qmm_set_trace(void* stamps) {
+    unsigned long long* p = static_cast<unsigned long long*>(stamps);
+    return cudaMemcpyToSymbol(tf::g_trace, &p, sizeof(p)) == cudaSuccess ? TF_OK : TF_ECUDA;
+}
 int tf_qmm_workers(void) { return tf::kWorkers; }
 
 size_t tf_qmm_tiled_bytes(int N, int K, int group) {
@@ -522,8 +540,7 @@ size_t tf_packed_bytes(int M, int K, int group) {
 }
 
 size_t tf_qmm_scratch_bytes(void) {
-    // counters + two parked partial blocks (128 rows x 256 columns fp32) per worker
-    return TF_QMM_COUNTER_BYTES + (size_t)2 * tf::kWorkers * TF_QMM_MAX_ROWS * tf::kCols * sizeof(float);
+    return tf::kScratchBytes;
 }
 
 int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N, int K,
@@ -533,7 +550,7 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
     if (!x_packed || !w_tiled || !y) return TF_EINVAL;
     const long long CB = (N + tf::kCols - 1) / tf::kCols, SPB = (K / 64 + tf::kItemTiles - 1) / tf::kItemTiles;
-    if (CB * 4 > TF_QMM_COUNTER_BYTES || CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
+    if (CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
     if ((uintptr_t)y & 3) return TF_EALIGN;
     if (!scratch || ((uintptr_t)scratch & 255)) return TF_ESCRATCH;
@@ -542,7 +559,8 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
     a.xp = static_cast<const uint8_t*>(x_packed);
     a.w = static_cast<const uint8_t*>(w_tiled);
     a.y = y;
-    a.counters = static_cast<int*>(scratch);
+    a.epochs = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kEpochOffset);
+    a.tags = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kTagOffset);
     a.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + TF_QMM_COUNTER_BYTES);
     a.status = status;
     a.M = M; a.N = N; a.K = K;
@@ -561,7 +579,7 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
     if (!x_packed || !w_tiled || !y || !prob_expert || !prob_count) return TF_EINVAL;
     const long long CB = (N + tf::kCols - 1) / tf::kCols;     // one schedule item per (problem, column block)
-    if (CB * max_probs * 4 > TF_QMM_COUNTER_BYTES || CB * max_probs > (1 << 30) / tf::kWorkers) return TF_EINVAL;
+    if (CB * max_probs > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
     if ((uintptr_t)y & 3) return TF_EALIGN;
     if (!scratch || ((uintptr_t)scratch & 255)) return TF_ESCRATCH;
@@ -570,7 +588,8 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.xp = static_cast<const uint8_t*>(x_packed);
     a.w = static_cast<const uint8_t*>(w_tiled);
     a.y = y;
-    a.counters = static_cast<int*>(scratch);
+    a.epochs = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kEpochOffset);
+    a.tags = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kTagOffset);
     a.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + TF_QMM_COUNTER_BYTES);
     a.status = status;
     a.M = 8; a.N = N; a.K = K;
@@ -580,8 +599,7 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return group == 64 ? tf::launch<64, 1, 4, tf::stages_for<64, 1, 4>(), true>(a, st)
-                       : tf::launch<32, 1, 4, tf::stages_for<32, 1, 4>(), true>(a, st);
+    return group == 64 ? tf::launch<tf::Cfg<64, 1, 4, 1, 1>, true>(a, st) : tf::launch<tf::Cfg<32, 1, 4, 1, 1>, true>(a, st);
 }
 
 int tf_qmm_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,

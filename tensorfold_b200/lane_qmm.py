@@ -177,7 +177,7 @@ _scratch: dict[tuple[int, int], torch.Tensor] = {}
 
 
 def scratch_for(device: torch.device) -> torch.Tensor:
-    """Per (device, stream) matmul scratch: zeroed counters + parked partial blocks."""
+    """Per (device, stream) matmul scratch (zeroed once): parked K segments, their ready tags, launch numbers."""
 
     key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(key)

@@ -109,14 +109,19 @@ def test_fp32_partial_rounds_to_the_bf16_output(qmm):
     assert_same_bits(p.to(torch.bfloat16), y, "fp32 partial")
 
 
-def test_given_group_sums_and_counters_left_zero(qmm):
+def test_rows_packed_by_the_caller_and_launch_numbers_in_step(qmm):
     x, words, scales, biases = make(1024, 5120, 64, seed=4, rows=8)
     q = qmm.tile_weight(words.cuda(), scales.cuda(), biases.cuda(), 64)
     xc = x.cuda()
     packed = qmm.pack_rows(xc)
     assert_same_bits(qmm.lane_matmul(packed, q), qmm.lane_matmul(xc, q), "rows packed by the caller")
     torch.cuda.synchronize()
-    assert int(qmm.scratch_for(xc.device)[:16384].view(torch.int32).abs().sum()) == 0
+    # every worker advanced its launch number once per call: they stay equal (what the K-segment tags rely on)
+    scratch = qmm.scratch_for(xc.device)
+    off = 16384 + 2 * 148 * 128 * 256 * 4
+    epochs = scratch[off:off + 148 * 4].view(torch.int32).cpu()
+    assert int(epochs.min()) == int(epochs.max()) and int(epochs[0]) > 0
+    assert int(scratch[:16384].view(torch.int32).abs().sum()) == 0         # the prefill kernel's ticket words
 
 
 def test_wrong_arguments_raise(qmm):
