@@ -66,10 +66,20 @@ size_t tf_packed_bytes(int M, int K, int group);
 int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
            int K, int group, int flags, int* status, void* stream);
 
-/* Profiling aid, no counterpart in the reference: with `stamps` not NULL (device memory, 148 * 8 uint64)
- * every later tf_qmm / tf_qmm_grouped launch on the current device writes eight %globaltimer values per
- * worker CTA (kernel entry, first weight copy issued, predecessor's memory visible, first stage ready,
- * main loop done, last segment parked, ordered sum done, last copy issued); NULL switches it off. */
+/* tf_qmm with a hint: next_w_tiled (may be NULL) is the tiled weight [next_N, next_K] of the matmul that the
+ * caller launches next on this stream. Once a worker has issued all of its own copies it asks L2 for the
+ * first bytes the same worker of that launch will stream, so the next matmul starts from L2 while this
+ * one finishes and the kernels between them run. Only a hint: results never depend on it. */
+int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
+                int K, int group, int flags, const void* next_w_tiled, int next_N, int next_K, int next_group, int* status,
+                void* stream);
+
+/* Profiling aid, no counterpart in the reference: with `stamps` not NULL (zeroed device memory of
+ * (148 + 512 * 148 * 16) uint64: a launch counter per worker, then a ring of the last 512 launches) every
+ * later tf_qmm / tf_qmm_grouped launch on the current device writes %globaltimer values per worker CTA:
+ * slot 0 kernel entry, 1 first weight copy issued, 2 predecessor's memory visible, 3 first stage ready,
+ * 4 main loop done, 5 first segment parked, 6 later segments added, 7 last copy issued, 9 last output
+ * written; NULL switches it off. */
 int tf_qmm_set_trace(void* stamps);
 
 /* Grouped form for mixture-of-experts layers: up to max_probs independent problems of 8 rows each in
@@ -212,6 +222,23 @@ int tf_gdn_replay(const void* k, const void* v, const float* g, const float* bet
                   long long rec_g_stride, long long state_stride, int k_heads, int v_heads, int dk, int dv,
                   void* stream);
 
+/* The whole GDN mixer between its two projections in ONE launch: causal conv + SiLU + q/k RMS scale +
+ * g/beta (tf_gdn_pre), the recurrence over each sequence's window rows (tf_gdn_chain) and the gated
+ * RMSNorm with SiLU(z) written as the output projection's packed input (tf_gated_norm). q, k, v, g, beta
+ * and y stay on chip; k, v, g, beta are also written to the record the commit replays. Every statement is
+ * the separate kernels', so the results have their bits. qkv [rows, 2*k_heads*128 + v_heads*128] conv
+ * input rows (qkv_stride elements a row), z [rows, v_heads*128], a, b [rows, v_heads] (ab_stride),
+ * conv_state [n_seqs, 3, C], conv_w [C, 4], norm_w [128], state [n_seqs, v_heads, 128, 128] fp32 (read
+ * only). out_packed: tf_packed_bytes(rows, v_heads*128, group) and/or out_rows [rows, v_heads*128] bf16.
+ * One CTA per (value head, sequence). rows <= 128.
+ * Replaces: families/qwen4_exp/cuda/gdn.cu:49-152 (the fused chain kernel) and, for the dense family,
+ * glue.py:48-130 + gdn_tree.cu:46-87 run back to back. */
+int tf_gdn_fused(const void* qkv, size_t qkv_stride, const void* z, size_t z_stride, const void* a, const void* b,
+                 size_t ab_stride, const void* conv_state, const void* conv_w, const float* a_log, const float* dt_bias,
+                 const void* norm_w, const float* state, void* k_out, void* v_out, float* g_out, float* beta_out,
+                 void* out_packed, void* out_rows, const int* seq_start, int rows, int n_seqs, int k_heads, int v_heads,
+                 int dk, int dv, int taps, int group, float eps, void* stream);
+
 /* Commit: conv_state[s] <- last 3 rows of [conv_state[s]; first keep[s] window rows of qkv].
  * Replaces: families/qwen3_5/cuda/forward.py:226-236 (conv rows in commit). */
 int tf_conv_commit(const void* qkv, size_t qkv_stride, long long rec_qkv_stride, void* conv_state,
@@ -222,18 +249,35 @@ int tf_conv_commit(const void* qkv, size_t qkv_stride, long long rec_qkv_stride,
  * Causal GQA for every window row of every sequence: row t of sequence s attends to the committed
  * tokens 0..seq_lens[s]-1 (pages: k_pages / v_pages [page, kv_head, 16, D] bf16 through
  * page_table [n_seqs, max_pages]) and to window rows 0..t of s (k_new / v_new [rows, kv_heads, D]).
- * Keys are cut by absolute position into 256-key chunks of 64-key tiles; per-chunk (m, l, O)
- * partials go to `scratch` (tf_attention_scratch_bytes) and are merged in chunk order.
- * row_nkeys[row] = seq_lens[s] + t + 1. max_window = longest window, max_chunks >= ceil(max over s of
- * (seq_lens[s] + window) / 512). q, out [rows, heads, D]; D = 128 or 256; heads/kv_heads <= 16.
+ * Keys are cut by absolute position into chunks of 64-key tiles (128 keys a chunk below position 8192,
+ * 512 up to 65536, 2048 beyond; tf_attention_chunks(n) = chunks holding keys 0..n-1); per-chunk
+ * (m, l, O) partials go to `scratch` (tf_attention_scratch_bytes) and are merged per row: four quarters
+ * of the row's chunks in order, then the quarters in order.
+ * row_nkeys[row] = seq_lens[s] + t + 1. max_window = longest window, max_chunks >= tf_attention_chunks(
+ * max over s of seq_lens[s] + window); a row that would need more chunks than max_chunks is merged
+ * over the first max_chunks only and TF_EINVAL is written to `status` (gated form), scratch is never
+ * read past its end. q, out [rows, heads, D]; D = 128 or 256; heads/kv_heads <= 16.
  * Replaces: families/qwen3_5/cuda/attention.py:152-201 (attention), families/qwen4_exp/cuda/attention.py:126-140,
  * kernels/qwen/dense/v1/lane_attention.py:430-518 (lane_sdpa, lane_tree_sdpa; chains only). */
 size_t tf_attention_scratch_bytes(int rows, int heads, int head_dim, int max_chunks);
+int tf_attention_chunks(int n_keys);
 int tf_lane_attention_paged(const void* q, const void* k_new, const void* v_new, const void* k_pages,
                             const void* v_pages, const int* page_table, int max_pages, const int* seq_lens,
                             const int* seq_start, const int* row_nkeys, void* out, void* scratch, size_t scratch_bytes,
                             int rows, int n_seqs, int max_window, int max_chunks, int heads, int kv_heads, int head_dim,
                             float scale, void* stream);
+
+/* The same attention with the layer's output gate and the next matmul's input fused into the merge:
+ * with qg not NULL (the q projection's output rows, per head [q_h ; gate_h], qg_stride elements a row)
+ * the result is bf16(o * sigmoid(gate)); with out_packed not NULL it is also written as the packed input
+ * of the output projection (tf_packed_bytes(rows, heads * D, group)) with its group sums; `out` may then
+ * be NULL. Replaces: families/qwen3_5/cuda/glue.py:206-226 (gate_mul) after the attention above. */
+int tf_lane_attention_paged_gated(const void* q, const void* k_new, const void* v_new, const void* k_pages,
+                                  const void* v_pages, const int* page_table, int max_pages, const int* seq_lens,
+                                  const int* seq_start, const int* row_nkeys, void* out, const void* qg, size_t qg_stride,
+                                  void* out_packed, int group, void* scratch, size_t scratch_bytes, int rows, int n_seqs,
+                                  int max_window, int max_chunks, int heads, int kv_heads, int head_dim, float scale,
+                                  int* status, void* stream);
 
 /* The same attention for callers that cannot allocate or pass scratch: a server whose device memory
  * was handed out once at start-up, a plugin inside a runtime that forbids allocation on the serving

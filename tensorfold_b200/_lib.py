@@ -29,6 +29,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p]),
     "tf_qmm_set_trace": (c_int, [c_void_p]),
+    "tf_qmm_next": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "tf_qmm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_int,
                                c_int, c_int, c_int, c_void_p, c_void_p]),
     "tf_pack_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -56,11 +58,19 @@ SIGNATURES: dict[str, tuple] = {
     "tf_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "tf_gdn_chain": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tf_gdn_fused": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "tf_gdn_replay": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                               c_longlong, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_void_p]),
     "tf_conv_commit": (c_int, [c_void_p, c_size_t, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int,
                                c_int, c_void_p]),
     "tf_attention_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tf_attention_chunks": (c_int, [c_int]),
+    "tf_lane_attention_paged_gated": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_void_p,
+                                              c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                              c_void_p]),
     "tf_lane_attention_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_float, c_void_p]),
@@ -92,7 +102,7 @@ SIGNATURES: dict[str, tuple] = {
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
 _NO_LAUNCH = {"tf_version", "tf_qmm_set_trace", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_peer_slot_bytes"}
+              "tf_attention_scratch_bytes", "tf_attention_chunks", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_peer_slot_bytes"}
 
 
 def launch_count() -> int:

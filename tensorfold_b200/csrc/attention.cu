@@ -2,11 +2,15 @@
 //
 // Keys of a sequence are its committed tokens (positions 0..L-1, read through the page table) followed
 // by the window's own rows (positions L.., read from the forward's uncommitted K/V rows); window row t
-// sees positions 0..L+t. The key axis is cut by ABSOLUTE position into 256-key chunks of four 64-key
-// tiles; one CTA handles (sequence, KV head, chunk) for all window rows and all query heads of that
-// KV head at once (rows of 16 = one tensor-core tile a warp), with an fp32 online softmax per query
-// row over the tiles in order, and writes per-chunk partials (m, l, O). A second kernel merges the
-// partials in chunk order. Every step of a query row's arithmetic is fixed by that row's own
+// sees positions 0..L+t. The key axis is cut by ABSOLUTE position into chunks of 64-key tiles: 128 keys
+// a chunk below position 8192, 512 up to 65536, 2048 beyond (short contexts still spread over the
+// whole GPU, long ones do not drown in partials); one CTA handles (sequence, KV head, chunk) for all
+// window rows and all query heads of that KV head at once (rows of 16 = one tensor-core tile a warp),
+// with an fp32 online softmax per query row over the tiles in order, and writes per-chunk partials
+// (m, l, O). A second kernel merges a row's partials: four warps take a quarter of the row's chunks
+// each, in order, and their results are combined in warp order; the quarters depend on the row's key
+// count only. It can also apply the layer's sigmoid output gate and write the output projection's
+// packed input. Every step of a query row's arithmetic is fixed by that row's own
 // (sequence, position): a row alone and the same row inside any window give the same bits, and a
 // serial step after committing t rows reads the same keys at the same positions as window row t.
 //
@@ -21,7 +25,22 @@
 namespace tf {
 namespace {
 
-constexpr int kChunk = 256, kTileKeys = 64, kPage = 16, kQRows = 64, kAttnWarps = 4;
+constexpr int kTileKeys = 64, kPage = 16, kQRows = 64, kAttnWarps = 4;
+// chunk c covers keys [chunk_begin(c), chunk_begin(c + 1)): a function of the absolute position only
+constexpr int kSmallKeys = 128, kSmallChunks = 64, kMidKeys = 512, kMidChunks = 112, kBigKeys = 2048;
+constexpr int kSmallEnd = kSmallKeys * kSmallChunks, kMidEnd = kSmallEnd + kMidKeys * kMidChunks;   // 8192, 65536
+__host__ __device__ inline int chunk_begin(int c) {
+    if (c < kSmallChunks) return c * kSmallKeys;
+    if (c < kSmallChunks + kMidChunks) return kSmallEnd + (c - kSmallChunks) * kMidKeys;
+    return kMidEnd + (c - kSmallChunks - kMidChunks) * kBigKeys;
+}
+// number of chunks that hold keys 0..n-1
+__host__ __device__ inline int chunks_for(int n) {
+    if (n <= 0) return 0;
+    if (n <= kSmallEnd) return (n + kSmallKeys - 1) / kSmallKeys;
+    if (n <= kMidEnd) return kSmallChunks + (n - kSmallEnd + kMidKeys - 1) / kMidKeys;
+    return kSmallChunks + kMidChunks + (n - kMidEnd + kBigKeys - 1) / kBigKeys;
+}
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnArgs {
@@ -72,7 +91,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_chunk_kernel(const AttnA
     const int nq = n * G;                      // query rows of this (sequence, KV head): row = t * G + head-in-group
     const int q0 = qg * kQRows;
     if (q0 >= nq) return;
-    const int key0 = chunk * kChunk;
+    const int key0 = chunk_begin(chunk), chunk_keys = chunk_begin(chunk + 1) - key0;
     if (key0 >= L + n) return;                 // nothing of this sequence in the chunk (partials are not read either)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 
@@ -84,26 +103,32 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_chunk_kernel(const AttnA
         cp_async16_zfill(smem_u32(q_s + swz<D>(r, c)), a.q + ((size_t)(r0 + wr) * a.H + kvh * G + hq) * D + c * 8, ok);
     }
     const int* pt = a.page_table + (size_t)seq * a.max_pages;
+    // A tile is four pages of 16 keys; warp w copies page w: the page number is looked up once, then
+    // every lane streams its own 16-byte column of the page's rows (K and V), so the per-copy address
+    // work is an add. Rows at or past the committed length come from the window's own K/V rows, rows
+    // past the last key are zero-filled.
     auto load_tile = [&](int tile, int buf) {
-        const int base = key0 + tile * kTileKeys;
-        for (int e = tid; e < kTileKeys * CPR; e += kAttnWarps * 32) {
-            const int r = e / CPR, c = e % CPR, p = base + r;
-            const __nv_bfloat16 *ksrc = a.k_new, *vsrc = a.v_new;
+        constexpr int RPI = 32 / CPR > 0 ? 32 / CPR : 1;      // rows a warp covers per step (1 for D = 256, 2 for D = 128)
+        const int base = key0 + tile * kTileKeys + warp * kPage;
+        const int c = lane % CPR, rsub = lane / CPR;
+        const bool any_old = base < L;
+        const size_t page_off = any_old ? ((size_t)pt[base / kPage] * a.HK + kvh) * kPage * D : 0;
+#pragma unroll 4
+        for (int rr = 0; rr < kPage; rr += RPI) {
+            const int r = rr + rsub, p = base + r;
             const bool ok = p < L + n;
+            size_t off = 0;
+            const __nv_bfloat16 *ksrc = a.k_new, *vsrc = a.v_new;
             if (ok) {
-                if (p < L) {
-                    const size_t off = (((size_t)pt[p / kPage] * a.HK + kvh) * kPage + (p % kPage)) * D + c * 8;
-                    ksrc = a.k_pages + off; vsrc = a.v_pages + off;
-                } else {
-                    const size_t off = ((size_t)(r0 + p - L) * a.HK + kvh) * D + c * 8;
-                    ksrc = a.k_new + off; vsrc = a.v_new + off;
-                }
+                if (p < L) { off = page_off + (size_t)r * D + c * 8; ksrc = a.k_pages; vsrc = a.v_pages; }
+                else off = ((size_t)(r0 + p - L) * a.HK + kvh) * D + c * 8;
             }
-            cp_async16_zfill(smem_u32(k_s + buf * TILEB + swz<D>(r, c)), ksrc, ok);
-            cp_async16_zfill(smem_u32(v_s + buf * TILEB + swz<D>(r, c)), vsrc, ok);
+            const uint32_t dst = swz<D>(warp * kPage + r, c);
+            cp_async16_zfill(smem_u32(k_s + buf * TILEB + dst), ksrc + off, ok);
+            cp_async16_zfill(smem_u32(v_s + buf * TILEB + dst), vsrc + off, ok);
         }
     };
-    const int ntiles = min(kChunk / kTileKeys, (L + n - key0 + kTileKeys - 1) / kTileKeys);
+    const int ntiles = min(chunk_keys / kTileKeys, (L + n - key0 + kTileKeys - 1) / kTileKeys);
     load_tile(0, 0);
     cp_async_commit();
 
@@ -213,34 +238,67 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_chunk_kernel(const AttnA
     }
 }
 
-// Merge the chunk partials of one (row, head) in chunk order; one warp each.
+// Merge the chunk partials of one (row, head): one CTA of four warps. Warp w merges chunks
+// [w * q, (w + 1) * q) of the row's nch chunks in order (q = ceil(nch / 4): a function of the row's key
+// count only), then the four results are combined in warp order. With `qg` the sigmoid output gate is
+// applied (gate values interleaved per head in the q projection: [q_h ; gate_h]) and with `out_packed`
+// the result is written as the output projection's packed input with its group sums.
+struct MergeArgs {
+    const float* part_o;
+    const float* part_m;
+    const float* part_l;
+    const int* row_nkeys;
+    __nv_bfloat16* out;            // [R, H, D] or null
+    const __nv_bfloat16* qg;       // gate source or null
+    size_t qg_stride;
+    uint8_t* out_packed;           // or null
+    int R, H, max_chunks, group;
+    int* status;
+};
+
 template <int D>
-__global__ void attn_merge_kernel(const float* part_o, const float* part_m, const float* part_l, const int* row_nkeys,
-                                  __nv_bfloat16* out, int R, int H) {
+__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeArgs a) {
+    constexpr int PER = D / 32, NW = 4;
+    static_assert(PER % 4 == 0, "a lane's slice is whole 16-byte loads");
+    __shared__ float sm_m[NW], sm_l[NW];
+    __shared__ __align__(16) float sm_o[NW][D];
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.y, head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (head >= H) return;
-    const int nch = (row_nkeys[row] + kChunk - 1) / kChunk;       // chunks holding keys this row can see
-    constexpr int PER = D / 32;
+    const int row = blockIdx.y, head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Mp = tf_padded_rows(a.R);
+    if (row >= a.R) {                                     // padding rows of the packed buffer are zero
+        if (a.out_packed != nullptr && warp == 0) {
+            const int c = head * (D / 8) + lane;
+            if (lane < D / 8) {
+                if (a.group == 64) packed_store<64>(a.out_packed, Mp, row, c, make_uint4(0, 0, 0, 0), 0.f);
+                else packed_store<32>(a.out_packed, Mp, row, c, make_uint4(0, 0, 0, 0), 0.f);
+            }
+        }
+        return;
+    }
+    int nch = chunks_for(a.row_nkeys[row]);
+    if (nch > a.max_chunks) {                             // the caller sized scratch for fewer chunks: never read past it
+        if (threadIdx.x == 0) report(a.status, TF_EINVAL);
+        nch = a.max_chunks;
+    }
+    const int quarter = (nch + NW - 1) / NW, c_lo = min(nch, warp * quarter), c_hi = min(nch, c_lo + quarter);
     float acc[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     // chunks are read four at a time (independent loads in flight together) and applied one by one in
-    // chunk order, so the arithmetic is that of the plain sequential merge
+    // chunk order, so the arithmetic is that of the plain sequential merge of the warp's range
     constexpr int B = 4;
-    static_assert(PER % 4 == 0, "a lane's slice is whole 16-byte loads");
-    for (int c0 = 0; c0 < nch; c0 += B) {
+    for (int c0 = c_lo; c0 < c_hi; c0 += B) {
         float cm[B], cl[B];
         float4 po[B][PER / 4];
 #pragma unroll
         for (int j = 0; j < B; ++j) {
-            const int c = min(c0 + j, nch - 1);
-            const size_t base = ((size_t)c * R + row) * H + head;
-            cm[j] = part_m[base];
-            cl[j] = c0 + j < nch ? part_l[base] : 0.f;
-            const float4* src = reinterpret_cast<const float4*>(part_o + base * D + lane * PER);
+            const int c = min(c0 + j, c_hi - 1);
+            const size_t base = ((size_t)c * a.R + row) * a.H + head;
+            cm[j] = a.part_m[base];
+            cl[j] = c0 + j < c_hi ? a.part_l[base] : 0.f;
+            const float4* src = reinterpret_cast<const float4*>(a.part_o + base * D + lane * PER);
 #pragma unroll
             for (int i = 0; i < PER / 4; ++i) po[j][i] = src[i];
         }
@@ -260,9 +318,60 @@ __global__ void attn_merge_kernel(const float* part_o, const float* part_m, cons
             m = mn;
         }
     }
-    __nv_bfloat16* dst = out + ((size_t)row * H + head) * D + lane * PER;
+    if (warp > 0) {
+        if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
-    for (int i = 0; i < PER; ++i) dst[i] = f2bf(acc[i] / l);
+        for (int i = 0; i < PER; ++i) sm_o[warp][lane * PER + i] = acc[i];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    for (int w = 1; w < NW; ++w) {                        // the later quarters, in order
+        const float cl = sm_l[w], cm = sm_m[w];
+        if (!(cl > 0.f)) continue;
+        const float mn = fmaxf(m, cm);
+        const float sa = exp2f(m - mn), sb = exp2f(cm - mn);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] = acc[i] * sa + sm_o[w][lane * PER + i] * sb;
+        l = l * sa + cl * sb;
+        m = mn;
+    }
+    float o[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) o[i] = round_bf16(acc[i] / l);
+    if (a.qg != nullptr) {
+        const __nv_bfloat16* gp = a.qg + (size_t)row * a.qg_stride + (size_t)head * 2 * D + D + lane * PER;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) o[i] = round_bf16(o[i] * sigmoidf_(bf2f(gp[i])));
+    }
+    if (a.out != nullptr) {
+        __nv_bfloat16* dst = a.out + ((size_t)row * a.H + head) * D + lane * PER;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) dst[i] = f2bf(o[i]);
+    }
+    if (a.out_packed != nullptr) {
+        // 8 values a chunk: D = 256 gives one chunk a lane; D = 128 (4 values a lane) pairs lanes up
+        if (PER == 8) {
+            const float o8[8] = {o[0], o[1], o[2], o[3], o[4 % PER], o[5 % PER], o[6 % PER], o[7 % PER]};
+            const uint4 v = pack8(o8);
+            const int c = head * (D / 8) + lane;
+            if (a.group == 64) { const float gs = group_sum8<64>(v); packed_store<64>(a.out_packed, Mp, row, c, v, gs); }
+            else { const float gs = group_sum8<32>(v); packed_store<32>(a.out_packed, Mp, row, c, v, gs); }
+        } else {
+            // lanes 2j and 2j+1 hold the two halves of chunk j: gather them in the even lane, then let lanes
+            // 0..15 act as the chunk's owners (the odd lanes' data moves down so that owners are contiguous)
+            float o8[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float mine = o[i % PER];
+                const float lo = __shfl_sync(0xffffffffu, mine, (2 * lane) & 31), hi = __shfl_sync(0xffffffffu, mine, (2 * lane + 1) & 31);
+                o8[i] = lo; o8[4 + i] = hi;
+            }
+            const uint4 v = lane < 16 ? pack8(o8) : make_uint4(0, 0, 0, 0);
+            const int c = head * (D / 8) + (lane & 15);
+            if (a.group == 64) { const float gs = group_sum8<64>(v); if (lane < 16) packed_store<64>(a.out_packed, Mp, row, c, v, gs); }
+            else { const float gs = group_sum8<32>(v); if (lane < 16) packed_store<32>(a.out_packed, Mp, row, c, v, gs); }
+        }
+    }
 }
 
 // Commit: copy each sequence's kept window rows into its pages at positions L.., for every layer.
@@ -285,23 +394,38 @@ __global__ void kv_commit_kernel(const __nv_bfloat16* k_new, const __nv_bfloat16
     }
 }
 
+struct GateArgs {
+    const void* qg = nullptr;      // q projection output with the per-head gates, or null
+    size_t qg_stride = 0;
+    void* out_packed = nullptr;
+    int group = 64;
+    int* status = nullptr;
+};
+
 template <int D>
-int run(const AttnArgs& a, int n_seqs, int max_chunks, const int* row_nkeys, void* out, cudaStream_t st) {
+int run(const AttnArgs& a, int n_seqs, int max_chunks, const int* row_nkeys, void* out, cudaStream_t st, const GateArgs& ga = GateArgs()) {
     constexpr size_t smem = (size_t)(kQRows + 4 * kTileKeys) * D * 2;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};       // the opt-in is per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return TF_ECUDA; }
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(attn_chunk_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return TF_ECUDA;
-        configured = true;
+        configured[dev] = true;
     }
     AttnArgs args = a;
     void* p1[] = {&args};
     if (launch_pdl((const void*)attn_chunk_kernel<D>, dim3(max_chunks, a.HK, n_seqs * a.qgroups), dim3(kAttnWarps * 32), smem,
                    st, p1) != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
-    const float *po = a.part_o, *pm = a.part_m, *pl = a.part_l;
-    int R = a.R, H = a.H;
-    void* p2[] = {&po, &pm, &pl, &row_nkeys, &out, &R, &H};
-    if (launch_pdl((const void*)attn_merge_kernel<D>, dim3((a.H + 3) / 4, a.R), dim3(128), 0, st, p2) != cudaSuccess) {
+    MergeArgs m;
+    m.part_o = a.part_o; m.part_m = a.part_m; m.part_l = a.part_l; m.row_nkeys = row_nkeys;
+    m.out = static_cast<__nv_bfloat16*>(out);
+    m.qg = static_cast<const __nv_bfloat16*>(ga.qg); m.qg_stride = ga.qg_stride;
+    m.out_packed = static_cast<uint8_t*>(ga.out_packed);
+    m.R = a.R; m.H = a.H; m.max_chunks = max_chunks; m.group = ga.group; m.status = ga.status;
+    void* p2[] = {&m};
+    const int grid_rows = ga.out_packed ? tf_padded_rows(a.R) : a.R;
+    if (launch_pdl((const void*)attn_merge_kernel<D>, dim3(a.H, grid_rows), dim3(128), 0, st, p2) != cudaSuccess) {
         cudaGetLastError(); return TF_ECUDA;
     }
     return TF_OK;
@@ -317,13 +441,28 @@ size_t tf_attention_scratch_bytes(int rows, int heads, int head_dim, int max_chu
     return (size_t)max_chunks * rows * heads * (head_dim + 2) * sizeof(float);
 }
 
+int tf_attention_chunks(int n_keys) { return tf::chunks_for(n_keys); }
+
 int tf_lane_attention_paged(const void* q, const void* k_new, const void* v_new, const void* k_pages, const void* v_pages,
                             const int* page_table, int max_pages, const int* seq_lens, const int* seq_start,
                             const int* row_nkeys, void* out, void* scratch, size_t scratch_bytes, int rows, int n_seqs,
                             int max_window, int max_chunks, int heads, int kv_heads, int head_dim, float scale, void* stream) {
+    return tf_lane_attention_paged_gated(q, k_new, v_new, k_pages, v_pages, page_table, max_pages, seq_lens, seq_start, row_nkeys,
+                                         out, nullptr, 0, nullptr, 64, scratch, scratch_bytes, rows, n_seqs, max_window,
+                                         max_chunks, heads, kv_heads, head_dim, scale, nullptr, stream);
+}
+
+int tf_lane_attention_paged_gated(const void* q, const void* k_new, const void* v_new, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int max_pages, const int* seq_lens, const int* seq_start,
+                                  const int* row_nkeys, void* out, const void* qg, size_t qg_stride, void* out_packed, int group,
+                                  void* scratch, size_t scratch_bytes, int rows, int n_seqs, int max_window, int max_chunks,
+                                  int heads, int kv_heads, int head_dim, float scale, int* status, void* stream) {
+    if (!out && !out_packed) return TF_EINVAL;
+    if ((group != 64 && group != 32) || (qg && qg_stride % 8) || (out_packed && rows > TF_QMM_MAX_ROWS)) return TF_EINVAL;
+    if (((uintptr_t)qg | (uintptr_t)out_packed | (uintptr_t)out) & 15) return TF_EALIGN;
     if (rows < 1 || n_seqs < 1 || max_window < 1 || max_chunks < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads) return TF_EINVAL;
     if ((head_dim != 128 && head_dim != 256) || heads / kv_heads > 16 || !(scale > 0.f)) return TF_EINVAL;
-    if (!q || !k_new || !v_new || !k_pages || !v_pages || !page_table || !seq_lens || !seq_start || !row_nkeys || !out) return TF_EINVAL;
+    if (!q || !k_new || !v_new || !k_pages || !v_pages || !page_table || !seq_lens || !seq_start || !row_nkeys) return TF_EINVAL;
     if (((uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return TF_EALIGN;
     if (!scratch || ((uintptr_t)scratch & 15) || scratch_bytes < tf_attention_scratch_bytes(rows, heads, head_dim, max_chunks))
         return TF_ESCRATCH;
@@ -341,8 +480,10 @@ int tf_lane_attention_paged(const void* q, const void* k_new, const void* v_new,
     a.scale_log2 = scale * tf::kLog2e;
     if ((long long)n_seqs * a.qgroups > 65535) return TF_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return head_dim == 256 ? tf::run<256>(a, n_seqs, max_chunks, row_nkeys, out, st)
-                           : tf::run<128>(a, n_seqs, max_chunks, row_nkeys, out, st);
+    tf::GateArgs ga;
+    ga.qg = qg; ga.qg_stride = qg_stride; ga.out_packed = out_packed; ga.group = group; ga.status = status;
+    return head_dim == 256 ? tf::run<256>(a, n_seqs, max_chunks, row_nkeys, out, st, ga)
+                           : tf::run<128>(a, n_seqs, max_chunks, row_nkeys, out, st, ga);
 }
 
 int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, void* k_pages, void* v_pages,

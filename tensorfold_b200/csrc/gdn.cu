@@ -153,6 +153,188 @@ __global__ void __launch_bounds__(kRowsPerCta * 4) gdn_kernel(const GdnArgs a) {
     }
 }
 
+// ---- the whole GDN mixer between its two projections, one launch ----------------------------------------
+// One CTA of 512 threads per (value head, sequence) does, for the sequence's window rows in passes of 8:
+//   1. the causal 4-tap conv + SiLU on the head's q, k and v channels, the RMS scale of q and k, the decay
+//      g and the write strength beta (one warp per (row, q | k | v), a lane's 4 channels: the statements of
+//      gdn_pre_kernel), into shared memory; k, v, g, beta also go to the record the commit replays;
+//   2. the delta-rule recurrence over the pass's rows with the fp32 state row in registers (4 lanes x 32
+//      values per value row: the statements of gdn_kernel), y rounded to bf16 into shared memory;
+//   3. the gated RMSNorm of y with SiLU(z) (16 lanes per row: the statements of gated_norm_kernel) written
+//      as the output projection's packed input with its group sums.
+// q, k, v, g, beta, y never travel through HBM between the steps and the three launches become one; every
+// statement is the unfused kernel's, so the results carry the same bits.
+struct GdnFusedArgs {
+    const __nv_bfloat16* qkv; size_t qkv_stride;      // [R, 2*KH*128 + VH*128] conv input rows
+    const __nv_bfloat16* z; size_t z_stride;          // [R, VH*128]
+    const __nv_bfloat16* a_in; const __nv_bfloat16* b_in; size_t ab_stride;   // [R, VH]
+    const __nv_bfloat16* conv_state;                  // [S, 3, C]
+    const __nv_bfloat16* conv_w;                      // [C, 4]
+    const float* a_log; const float* dt_bias;         // [VH]
+    const __nv_bfloat16* norm_w;                      // [128]
+    const float* state_in;                            // [S, VH, 128, 128]
+    __nv_bfloat16* k_out; __nv_bfloat16* v_out; float* g_out; float* beta_out;   // the record
+    uint8_t* out_packed; __nv_bfloat16* out_rows;     // [R, VH*128] packed (and optionally plain rows)
+    const int* seq_start;
+    int KH, VH, S, R, group;
+    float eps;
+};
+
+template <int G>
+__global__ void __launch_bounds__(512) gdn_fused_kernel(const GdnFusedArgs a) {
+    __shared__ float ks[kTile][kDk], qs[kTile][kDk], vs[kTile][kDk], ys[kTile][kDk];
+    __shared__ float gs[kTile], bs[kTile];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j = tid & 3, dvrow = tid >> 2;                       // recurrence roles: value row, quarter of the key axis
+    const int kh = head / (a.VH / a.KH);
+    const int C = (2 * a.KH + a.VH) * 128;
+    const int r0 = a.seq_start[seq], n = a.seq_start[seq + 1] - r0;
+    const int Mp = tf_padded_rows(a.R), total = a.VH * 16;         // chunks of 8 in an output row
+    // the last sequence's CTAs also zero the packed buffer's padding rows for their head
+    if (seq == a.S - 1 && a.out_packed != nullptr) {
+        for (int e = tid; e < (Mp - a.R) * 16; e += 512)
+            packed_store<G>(a.out_packed, Mp, a.R + e / 16, head * 16 + (e & 15), make_uint4(0, 0, 0, 0), 0.f);
+    }
+    if (n <= 0) return;
+    const size_t srow = (((size_t)seq * a.VH + head) * kDk + dvrow) * kDk;
+    float4 s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = reinterpret_cast<const float4*>(a.state_in + srow)[i * 4 + j];
+
+    for (int t0 = 0; t0 < n; t0 += kTile) {
+        const int rows = min(kTile, n - t0);
+        __syncthreads();
+        // ---- 1. conv + gates: task = (row of the pass, part) with part 0 = q, 1 = k, 2 = v ----
+        for (int task = warp; task < rows * 3; task += 16) {
+            const int r = task / 3, part = task - 3 * r;
+            const int row = r0 + t0 + r, idx = t0 + r;             // idx: the row's place in its sequence's chain
+            const int chead = part == 0 ? kh : part == 1 ? a.KH + kh : 2 * a.KH + head;
+            const int ch0 = chead * 128 + lane * 4;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float wt[16];
+            {
+                const uint4* wp = reinterpret_cast<const uint4*>(a.conv_w + (size_t)ch0 * 4);
+                float lo[8], hi[8];
+                unpack8(wp[0], lo);
+                unpack8(wp[1], hi);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { wt[i] = lo[i]; wt[8 + i] = hi[i]; }
+            }
+#pragma unroll
+            for (int tap = 0; tap < 4; ++tap) {
+                const int src = idx + tap;                         // index into [conv_state (3 rows); window rows]
+                const __nv_bfloat16* p = src < 3 ? a.conv_state + ((size_t)seq * 3 + src) * C + ch0
+                                                 : a.qkv + (size_t)(row - idx + src - 3) * a.qkv_stride + ch0;
+                const uint2 xv = *reinterpret_cast<const uint2*>(p);
+                const float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] = __fmaf_rn(xf[i], wt[i * 4 + tap], acc[i]);
+            }
+            float c[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[i] = round_bf16(acc[i] * sigmoidf_(acc[i]));
+            if (part < 2) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ss += c[i] * c[i];
+                const float inv = 1.0f / sqrtf(warp_sum(ss) / 128.0f + 1e-6f);
+                const float scale = part == 0 ? 1.0f / 128.0f : 0.08838834764831845f;   // 1/dk, dk^-1/2
+                const uint2 packed = make_uint2(pack_bf16(c[0] * inv * scale, c[1] * inv * scale),
+                                                pack_bf16(c[2] * inv * scale, c[3] * inv * scale));
+                float* dst = (part == 0 ? qs[r] : ks[r]) + lane * 4;
+                dst[0] = bf16_lo(packed.x); dst[1] = bf16_hi(packed.x); dst[2] = bf16_lo(packed.y); dst[3] = bf16_hi(packed.y);
+                // one of the value heads that share this key head keeps k for the commit
+                if (part == 1 && head % (a.VH / a.KH) == 0)
+                    *reinterpret_cast<uint2*>(a.k_out + ((size_t)row * a.KH + kh) * 128 + lane * 4) = packed;
+            } else {
+                const uint2 packed = make_uint2(pack_bf16(c[0], c[1]), pack_bf16(c[2], c[3]));
+                float* dst = vs[r] + lane * 4;
+                dst[0] = c[0]; dst[1] = c[1]; dst[2] = c[2]; dst[3] = c[3];
+                *reinterpret_cast<uint2*>(a.v_out + ((size_t)row * a.VH + head) * 128 + lane * 4) = packed;
+                if (lane == 0) {
+                    const float av = bf2f(a.a_in[(size_t)row * a.ab_stride + head]) + a.dt_bias[head];
+                    const float sp = av > 20.0f ? av : logf(1.0f + expf(av));
+                    const float gv = expf(-expf(a.a_log[head]) * sp);
+                    const float bv = sigmoidf_(bf2f(a.b_in[(size_t)row * a.ab_stride + head]));
+                    gs[r] = gv; bs[r] = bv;
+                    a.g_out[(size_t)row * a.VH + head] = gv;
+                    a.beta_out[(size_t)row * a.VH + head] = bv;
+                }
+            }
+        }
+        __syncthreads();
+        // ---- 2. recurrence over the pass's rows ----
+        for (int r = 0; r < rows; ++r) {
+            const float decay = gs[r];
+            float mem = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
+                s[i].x *= decay; s[i].y *= decay; s[i].z *= decay; s[i].w *= decay;
+                mem = __fmaf_rn(s[i].x, kv.x, mem);
+                mem = __fmaf_rn(s[i].y, kv.y, mem);
+                mem = __fmaf_rn(s[i].z, kv.z, mem);
+                mem = __fmaf_rn(s[i].w, kv.w, mem);
+            }
+            mem += __shfl_xor_sync(0xffffffffu, mem, 1);
+            mem += __shfl_xor_sync(0xffffffffu, mem, 2);
+            const float delta = (vs[r][dvrow] - mem) * bs[r];
+            float out = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
+                const float4 qv = *reinterpret_cast<const float4*>(&qs[r][i * 16 + j * 4]);
+                s[i].x = __fmaf_rn(kv.x, delta, s[i].x);
+                s[i].y = __fmaf_rn(kv.y, delta, s[i].y);
+                s[i].z = __fmaf_rn(kv.z, delta, s[i].z);
+                s[i].w = __fmaf_rn(kv.w, delta, s[i].w);
+                out = __fmaf_rn(s[i].x, qv.x, out);
+                out = __fmaf_rn(s[i].y, qv.y, out);
+                out = __fmaf_rn(s[i].z, qv.z, out);
+                out = __fmaf_rn(s[i].w, qv.w, out);
+            }
+            out += __shfl_xor_sync(0xffffffffu, out, 1);
+            out += __shfl_xor_sync(0xffffffffu, out, 2);
+            if (j == 0) ys[r][dvrow] = round_bf16(out);
+        }
+        __syncthreads();
+        // ---- 3. gated norm + packing: 16 lanes per row, 8 values a lane ----
+        if (warp * 2 < rows) {
+            const int r = warp * 2 + (lane >> 4), l16 = lane & 15;
+            const bool live = r < rows;
+            const int row = r0 + t0 + (live ? r : 0);
+            float yv[8], zv[8], wv[8], o[8];
+            float ss = 0.f;
+            uint4 ov = make_uint4(0, 0, 0, 0);
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) yv[i] = ys[r][l16 * 8 + i];
+                unpack8(*reinterpret_cast<const uint4*>(a.z + (size_t)row * a.z_stride + head * 128 + 8 * l16), zv);
+                unpack8(reinterpret_cast<const uint4*>(a.norm_w)[l16], wv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss += yv[i] * yv[i];
+            }
+#pragma unroll
+            for (int o2 = 1; o2 < 16; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+            if (live) {
+                const float inv = 1.0f / sqrtf(ss / 128.0f + a.eps);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = zv[i] * sigmoidf_(zv[i]) * (yv[i] * inv * wv[i]);
+                ov = pack8(o);
+            }
+            const float gsum = group_sum8<G>(ov);
+            if (live) {
+                const int c = head * 16 + l16;
+                if (a.out_rows != nullptr) reinterpret_cast<uint4*>(a.out_rows)[(size_t)row * total + c] = ov;
+                if (a.out_packed != nullptr) packed_store<G>(a.out_packed, Mp, row, c, ov, gsum);
+            }
+        }
+    }
+}
+
 // Conv tail after a commit: the last 3 rows of [old tail (3 rows); the sequence's kept window rows].
 __global__ void conv_commit_kernel(const __nv_bfloat16* qkv, size_t qkv_stride, long long rec_qkv, __nv_bfloat16* conv_state,
                                    long long rec_state, const int* seq_start, const int* keep, int C, int S) {
@@ -203,6 +385,33 @@ int tf_gdn_chain(const void* q, const void* k, const void* v, const float* g, co
     dim3 grid((dv + tf::kRowsPerCta - 1) / tf::kRowsPerCta, v_heads, n_seqs);
     cudaError_t e = tf::launch_pdl((const void*)tf::gdn_kernel<true>, grid, dim3(tf::kRowsPerCta * 4), 0,
                                    static_cast<cudaStream_t>(stream), args);
+    if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
+    return TF_OK;
+}
+
+int tf_gdn_fused(const void* qkv, size_t qkv_stride, const void* z, size_t z_stride, const void* a, const void* b, size_t ab_stride,
+                 const void* conv_state, const void* conv_w, const float* a_log, const float* dt_bias, const void* norm_w,
+                 const float* state, void* k_out, void* v_out, float* g_out, float* beta_out, void* out_packed, void* out_rows,
+                 const int* seq_start, int rows, int n_seqs, int k_heads, int v_heads, int dk, int dv, int taps, int group, float eps,
+                 void* stream) {
+    if (rows < 1 || rows > TF_QMM_MAX_ROWS || n_seqs < 1 || n_seqs > 65535 || k_heads < 1 || v_heads < 1 || v_heads % k_heads) return TF_EINVAL;
+    if (dk != 128 || dv != 128 || taps != 4 || (group != 64 && group != 32)) return TF_EINVAL;
+    if (!qkv || !z || !a || !b || !conv_state || !conv_w || !a_log || !dt_bias || !norm_w || !state || !seq_start) return TF_EINVAL;
+    if (!k_out || !v_out || !g_out || !beta_out || (!out_packed && !out_rows) || qkv_stride % 4 || z_stride % 8) return TF_EINVAL;
+    if (((uintptr_t)qkv | (uintptr_t)conv_state | (uintptr_t)k_out | (uintptr_t)v_out) & 7) return TF_EALIGN;
+    if (((uintptr_t)conv_w | (uintptr_t)z | (uintptr_t)norm_w | (uintptr_t)state | (uintptr_t)out_packed | (uintptr_t)out_rows) & 15) return TF_EALIGN;
+    tf::GdnFusedArgs g = {};
+    g.qkv = static_cast<const __nv_bfloat16*>(qkv); g.qkv_stride = qkv_stride;
+    g.z = static_cast<const __nv_bfloat16*>(z); g.z_stride = z_stride;
+    g.a_in = static_cast<const __nv_bfloat16*>(a); g.b_in = static_cast<const __nv_bfloat16*>(b); g.ab_stride = ab_stride;
+    g.conv_state = static_cast<const __nv_bfloat16*>(conv_state); g.conv_w = static_cast<const __nv_bfloat16*>(conv_w);
+    g.a_log = a_log; g.dt_bias = dt_bias; g.norm_w = static_cast<const __nv_bfloat16*>(norm_w); g.state_in = state;
+    g.k_out = static_cast<__nv_bfloat16*>(k_out); g.v_out = static_cast<__nv_bfloat16*>(v_out); g.g_out = g_out; g.beta_out = beta_out;
+    g.out_packed = static_cast<uint8_t*>(out_packed); g.out_rows = static_cast<__nv_bfloat16*>(out_rows);
+    g.seq_start = seq_start; g.KH = k_heads; g.VH = v_heads; g.S = n_seqs; g.R = rows; g.group = group; g.eps = eps;
+    void* args[] = {&g};
+    const void* fn = group == 64 ? (const void*)tf::gdn_fused_kernel<64> : (const void*)tf::gdn_fused_kernel<32>;
+    cudaError_t e = tf::launch_pdl(fn, dim3(v_heads, n_seqs), dim3(512), 0, static_cast<cudaStream_t>(stream), args);
     if (e != cudaSuccess) { cudaGetLastError(); return TF_ECUDA; }
     return TF_OK;
 }

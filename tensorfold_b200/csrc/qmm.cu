@@ -84,8 +84,8 @@ __device__ __forceinline__ unsigned long long now_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-constexpr int kTraceLaunches = 32, kTraceSlots = 16;
-// layout: [148] per-CTA launch counters, then [launch % 32][cta][16] stamps
+constexpr int kTraceLaunches = 512, kTraceSlots = 16;
+// layout: [148] per-CTA launch counters, then [launch % 512][cta][16] stamps
 __device__ __forceinline__ void stamp(unsigned long long* tr, int slot) {
     if (tr != nullptr) tr[blockIdx.x * kTraceSlots + slot] = now_ns();
 }
@@ -95,7 +95,6 @@ struct Args {
     const uint8_t* w;
     void* y;
     uint32_t* epochs;
-    uint32_t* tags;
     float* slots;
     int* status;
     int M, N, K;
@@ -105,6 +104,10 @@ struct Args {
     // into y + p * y_stride elements; the live count is read on the device. nullptr: one problem.
     // With prob_sel, the launch covers the problems prob_sel[0 .. count) only (an expert-parallel rank's
     // own experts); addresses are still formed from the selected problem's index.
+    // the matmul that runs next on this stream (may be null): once this kernel's own copies are all
+    // issued, each worker asks L2 for the first bytes the SAME worker of that launch will stream
+    const uint8_t* next_w;
+    int next_N, next_K, next_group, prefetch_bytes;
     const int* prob_expert;
     const int* prob_count;
     const int* prob_sel;
@@ -117,19 +120,15 @@ struct Args {
 __host__ __device__ inline int range_begin(int cta, int total) { return (int)((unsigned)cta * (unsigned)total / (unsigned)kWorkers); }
 
 constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
-constexpr int kMaxThreads = 512;          // consumer threads of the widest configuration
-// scratch: [ticket words of the prefill kernel][parked segments, two slots a worker (this kernel uses one)]
-//          [launch numbers, one a worker][ready tags, one per worker and consumer thread]
+// scratch: [ticket words of the prefill kernel][parked segments, one slot of 2 x 128 x 256 floats a worker]
+//          [launch numbers, one a worker]
 constexpr size_t kEpochOffset = TF_QMM_COUNTER_BYTES + 2 * kWorkers * kSlotFloats * sizeof(float);
-constexpr size_t kTagOffset = kEpochOffset + 1024;
-constexpr size_t kScratchBytes = kTagOffset + (size_t)kWorkers * kMaxThreads * sizeof(uint32_t);
+constexpr size_t kScratchBytes = kEpochOffset + 1024;
 
-__device__ __forceinline__ void st_release(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// 16-byte load that is performed every time it is executed (a polled location)
+__device__ __forceinline__ float4 ld_volatile16(const float4* p) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -137,14 +136,17 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
 // segments belong to consecutive workers: the first segment (the block's first k items) ends one
 // worker's range, every later segment starts the next worker's range. A worker therefore "parks" at
 // most one segment, the first of its range, early in the kernel: each consumer thread stores its
-// accumulators (its own float4s, thread-major, so the stores coalesce) and then a tag carrying the
-// launch number with release order. The worker that holds the block's FIRST segment is the one that
-// finishes the block: at the end of its range it keeps that segment in registers, waits (bounded) for
-// the tags of the later segments, which were parked long before unless their worker started late, adds
-// them in worker order, which is k order, and writes the output. No tickets, no fences on the critical
-// path, and nothing to reset. The launch number is the worker's own counter in scratch, advanced once
+// accumulators as 16-byte packets {value, value, launch number, launch number} (thread-major, so the
+// stores coalesce; a packet is stored whole, so whoever reads this launch's number in it has the values).
+// The worker that holds the block's FIRST segment is the one that finishes the block: at the end of its
+// range it keeps that segment in registers, fetches the later segments' packets (again, bounded, while
+// one still carries an older number), which were parked long before unless their worker started late,
+// adds them in worker order, which is k order, and writes the output. No tickets, flags or fences, one
+// round trip on the critical path, and nothing to reset. The launch number is the worker's own counter in scratch, advanced once
 // per launch before dependents may start, so every worker of a launch holds the same number.
-template <class C, bool MULTI>
+// FULL: K is a whole number of pipeline stages, so every stage holds KTS k tiles and the loop over them
+// carries no test (the compiler then interleaves the tiles' instruction streams).
+template <class C, bool MULTI, bool FULL>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) {
     constexpr int MB = C::MB, KTS = C::KTS, STAGES = C::STAGES, CW = C::CW, T = C::T, NC = CW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -225,6 +227,22 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
                 it = seg_end;
             }
             stamp(tr, 7);
+            if (a.next_w != nullptr) {
+                // where this worker's range of the next matmul starts (its items are cut like this one's)
+                const int nKT = a.next_K >> 6, nCB = (a.next_N + kCols - 1) / kCols, nSPB = (nKT + kItemTiles - 1) / kItemTiles;
+                const int ntotal = nCB * nSPB;
+                const int nb = range_begin(blockIdx.x, ntotal), ne = range_begin(blockIdx.x + 1, ntotal);
+                const size_t tile_bytes = (size_t)kWarps * rec_bytes(a.next_group);      // one k tile of a column block
+                const size_t at = ((size_t)(nb / nSPB) * nKT + (size_t)(nb % nSPB) * kItemTiles) * tile_bytes;
+                const size_t whole = (size_t)nCB * nKT * tile_bytes;
+                size_t len = (size_t)(ne - nb) * kItemTiles * tile_bytes;
+                if (len > (size_t)a.prefetch_bytes) len = (size_t)a.prefetch_bytes;
+                if (at + len > whole) len = whole > at ? whole - at : 0;
+                for (size_t off = 0; off < len; off += 32768) {
+                    const uint32_t piece = (uint32_t)(len - off < 32768 ? len - off : 32768);
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next_w + at + off), "r"(piece) : "memory");
+                }
+            }
             if (!waited) {
                 pdl_wait();
                 for (int e = 0; e < issued; ++e)
@@ -269,7 +287,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             const uint8_t* xst = sb + C::W_BYTES;
 #pragma unroll
             for (int kt = 0; kt < KTS; ++kt) {
-                if (kt < nkt) {
+                if (FULL || kt < nkt) {
                     const uint8_t* xt = xst + kt * C::XTILE;
                     const float* xsums = reinterpret_cast<const float*>(xt + C::ROWS * 128) + 2 * t;
                     uint32_t af[T][4][4];
@@ -326,40 +344,70 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
         if (tr != nullptr && threadIdx.x == 0 && seg_end == end) stamp(tr, 4);
         if (seg_begin > cb_begin) {
             // a later segment of a block some earlier worker finishes: park it (always the first of this range)
-            float4* slot = reinterpret_cast<float4*>(a.slots + (size_t)blockIdx.x * kSlotFloats);
+            // as 16-byte packets {value, value, launch number, launch number}: a packet is stored whole, so a
+            // reader that sees this launch's number in it has the values too. No fence, no flag.
+            float4* slot = reinterpret_cast<float4*>(a.slots + (size_t)blockIdx.x * (2 * kSlotFloats));
+            const float tagf = __uint_as_float(epoch);
 #pragma unroll
             for (int ti = 0; ti < T; ++ti)
 #pragma unroll
-                for (int rb = 0; rb < MB; ++rb)
-                    __stcg(slot + (ti * MB + rb) * NC + threadIdx.x,
-                           make_float4(acc[ti][rb][0], acc[ti][rb][1], acc[ti][rb][2], acc[ti][rb][3]));
-            st_release(a.tags + (size_t)blockIdx.x * kMaxThreads + threadIdx.x, epoch);
+                for (int rb = 0; rb < MB; ++rb) {
+                    __stcg(slot + ((ti * MB + rb) * 2 + 0) * NC + threadIdx.x, make_float4(acc[ti][rb][0], acc[ti][rb][1], tagf, tagf));
+                    __stcg(slot + ((ti * MB + rb) * 2 + 1) * NC + threadIdx.x, make_float4(acc[ti][rb][2], acc[ti][rb][3], tagf, tagf));
+                }
             if (tr != nullptr && threadIdx.x == 0) stamp(tr, 5);
             continue;
         }
         if (seg_end < cb_end) {
-            // the block's first segment: add the later ones, parked by the next workers, in worker order
-            for (int o = blockIdx.x + 1; o < kWorkers; ++o) {
-                const int ob = range_begin(o, total);
-                if (ob >= cb_end) break;
-                if (range_begin(o + 1, total) == ob) continue;       // a worker without work
-                const uint32_t* tag = a.tags + (size_t)o * kMaxThreads + threadIdx.x;
+            // the block's first segment: add the later ones, parked by the next workers, in worker order.
+            // Up to four segments are waited for and fetched together (their latencies overlap) and then
+            // added one by one, so the sum is the plain sequential one.
+            int o = blockIdx.x + 1;
+            bool more = true;
+            while (more) {
+                constexpr int SB = 4;
+                int who[SB], cnt = 0;
+                for (; o < kWorkers && cnt < SB; ++o) {
+                    const int ob = range_begin(o, total);
+                    if (ob >= cb_end) { more = false; break; }
+                    if (range_begin(o + 1, total) == ob) continue;       // a worker without work
+                    who[cnt++] = o;
+                }
+                if (o >= kWorkers) more = false;
+                if (cnt == 0) break;
+                // fetch every packet of the batch; a packet that does not carry this launch's number yet is
+                // fetched again (bounded)
+                float4 v[SB][T][MB][2];
                 bool ready = false;
-                for (int spin = 0; spin < (1 << 20); ++spin)
-                    if (ld_acquire(tag) == epoch) { ready = true; break; }
+                for (int spin = 0; spin < (1 << 20) && !ready; ++spin) {
+                    ready = true;
+#pragma unroll
+                    for (int j = 0; j < SB; ++j)
+                        if (j < cnt) {
+                            const float4* slot = reinterpret_cast<const float4*>(a.slots + (size_t)who[j] * (2 * kSlotFloats));
+#pragma unroll
+                            for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+                                for (int rb = 0; rb < MB; ++rb)
+#pragma unroll
+                                    for (int h = 0; h < 2; ++h) {
+                                        const float4 pk = ld_volatile16(slot + ((ti * MB + rb) * 2 + h) * NC + threadIdx.x);
+                                        v[j][ti][rb][h] = pk;
+                                        ready = ready && __float_as_uint(pk.z) == epoch && __float_as_uint(pk.w) == epoch;
+                                    }
+                        }
+                }
                 if (!ready) report(a.status, TF_ESTALL);
-                const float4* slot = reinterpret_cast<const float4*>(a.slots + (size_t)o * kSlotFloats);
-                float4 v[T][MB];
 #pragma unroll
-                for (int ti = 0; ti < T; ++ti)
+                for (int j = 0; j < SB; ++j)
+                    if (j < cnt) {
 #pragma unroll
-                    for (int rb = 0; rb < MB; ++rb) v[ti][rb] = __ldcg(slot + (ti * MB + rb) * NC + threadIdx.x);
+                        for (int ti = 0; ti < T; ++ti)
 #pragma unroll
-                for (int ti = 0; ti < T; ++ti)
-#pragma unroll
-                    for (int rb = 0; rb < MB; ++rb) {
-                        acc[ti][rb][0] += v[ti][rb].x; acc[ti][rb][1] += v[ti][rb].y;
-                        acc[ti][rb][2] += v[ti][rb].z; acc[ti][rb][3] += v[ti][rb].w;
+                            for (int rb = 0; rb < MB; ++rb) {
+                                acc[ti][rb][0] += v[j][ti][rb][0].x; acc[ti][rb][1] += v[j][ti][rb][0].y;
+                                acc[ti][rb][2] += v[j][ti][rb][1].x; acc[ti][rb][3] += v[j][ti][rb][1].y;
+                            }
                     }
             }
             if (tr != nullptr && threadIdx.x == 0) stamp(tr, 6);
@@ -384,10 +432,18 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
     if (threadIdx.x == 0) stamp(tr, 9);
 }
 
+template <class C, bool MULTI, bool FULL>
+int launch_as(const Args& a, cudaStream_t stream);
+
 template <class C, bool MULTI = false>
 int launch(const Args& a, cudaStream_t stream) {
+    return (a.K / 64) % C::KTS == 0 ? launch_as<C, MULTI, true>(a, stream) : launch_as<C, MULTI, false>(a, stream);
+}
+
+template <class C, bool MULTI, bool FULL>
+int launch_as(const Args& a, cudaStream_t stream) {
     static_assert(C::SMEM <= (C::CTAS == 2 ? 113 : 227) * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<C, MULTI>;
+    auto kern = qmm_kernel<C, MULTI, FULL>;
     // the opt-in is per device: keep one flag per device ordinal
     static bool configured[64] = {};
     int dev = 0;
@@ -411,24 +467,19 @@ int launch(const Args& a, cudaStream_t stream) {
     return TF_OK;
 }
 
-inline int variant() {
-    static const int v = [] { const char* e = std::getenv("TF_QMM_VARIANT"); return e ? atoi(e) : 0; }();
+// bytes of the next matmul's weight each worker asks L2 for (TF_QMM_PREFETCH_KB, default the ring's size)
+inline int prefetch_bytes() {
+    static const int v = [] { const char* e = std::getenv("TF_QMM_PREFETCH_KB"); return (e ? atoi(e) : 224) * 1024; }();
     return v;
 }
 
 template <int G>
 int dispatch(const Args& a, cudaStream_t stream) {
-    if (a.M <= 8) {
-        switch (variant()) {
-            case 1: return launch<Cfg<G, 1, 4, 2, 1>>(a, stream);
-            case 2: return launch<Cfg<G, 1, 2, 2, 2>>(a, stream);
-            case 3: return launch<Cfg<G, 1, 2, 1, 1>>(a, stream);
-            case 4: return launch<Cfg<G, 1, 2, 2, 1>>(a, stream);
-            case 5: return launch<Cfg<G, 1, 2, 1, 2>>(a, stream);
-            default: return launch<Cfg<G, 1, 4, 1, 1>>(a, stream);
-        }
-    }
-    if (a.M <= 16) return launch<Cfg<G, 2, 4, 1, 1>>(a, stream);
+    // up to 16 rows the kernel streams from HBM: a warp takes two column tiles, which share the activation
+    // loads; the wider buckets are bound by the tensor pipe and keep one tile a warp (their accumulators
+    // take the registers)
+    if (a.M <= 8) return launch<Cfg<G, 1, 4, 2, 1>>(a, stream);
+    if (a.M <= 16) return launch<Cfg<G, 2, 4, 2, 1>>(a, stream);
     if (a.M <= 32) return launch<Cfg<G, 4, 4, 1, 1>>(a, stream);
     if (a.M <= 64) return launch<Cfg<G, 8, 2, 1, 1>>(a, stream);
     return launch<Cfg<G, 16, 2, 1, 1>>(a, stream);
@@ -545,6 +596,13 @@ size_t tf_qmm_scratch_bytes(void) {
 
 int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N, int K,
            int group, int flags, int* status, void* stream) {
+    return tf_qmm_next(x_packed, w_tiled, y, scratch, scratch_bytes, M, N, K, group, flags, nullptr, 0, 0, 0, status, stream);
+}
+
+int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N, int K,
+                int group, int flags, const void* next_w_tiled, int next_N, int next_K, int next_group, int* status, void* stream) {
+    if (next_w_tiled && (next_N < 1 || next_K < 64 || next_K % 64 || (next_group != 64 && next_group != 32) || ((uintptr_t)next_w_tiled & 15)))
+        return TF_EINVAL;
     if (M < 1 || M > TF_QMM_MAX_ROWS || N < 1 || K < 64 || K % 64) return TF_EINVAL;
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
@@ -560,13 +618,14 @@ int tf_qmm(const void* x_packed, const void* w_tiled, void* y, void* scratch, si
     a.w = static_cast<const uint8_t*>(w_tiled);
     a.y = y;
     a.epochs = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kEpochOffset);
-    a.tags = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kTagOffset);
     a.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + TF_QMM_COUNTER_BYTES);
     a.status = status;
     a.M = M; a.N = N; a.K = K;
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
     a.prob_expert = nullptr; a.prob_count = nullptr; a.prob_sel = nullptr; a.max_probs = 1;
     a.w_stride = a.xp_stride = a.y_stride = 0;
+    a.next_w = static_cast<const uint8_t*>(next_w_tiled); a.next_N = next_N; a.next_K = next_K; a.next_group = next_group;
+    a.prefetch_bytes = tf::prefetch_bytes();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return group == 64 ? tf::dispatch<64>(a, st) : tf::dispatch<32>(a, st);
 }
@@ -589,17 +648,17 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.w = static_cast<const uint8_t*>(w_tiled);
     a.y = y;
     a.epochs = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kEpochOffset);
-    a.tags = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + tf::kTagOffset);
     a.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + TF_QMM_COUNTER_BYTES);
     a.status = status;
     a.M = 8; a.N = N; a.K = K;
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
     a.prob_expert = prob_expert; a.prob_count = prob_count; a.prob_sel = prob_sel; a.max_probs = max_probs;
+    a.next_w = nullptr; a.next_N = a.next_K = a.next_group = a.prefetch_bytes = 0;
     a.w_stride = (long long)tf_qmm_tiled_bytes(N, K, group);
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return group == 64 ? tf::launch<tf::Cfg<64, 1, 4, 1, 1>, true>(a, st) : tf::launch<tf::Cfg<32, 1, 4, 1, 1>, true>(a, st);
+    return group == 64 ? tf::launch<tf::Cfg<64, 1, 4, 2, 1>, true>(a, st) : tf::launch<tf::Cfg<32, 1, 4, 2, 1>, true>(a, st);
 }
 
 int tf_qmm_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,

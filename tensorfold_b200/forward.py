@@ -203,7 +203,7 @@ def refresh_batch(b: Batch, st: State) -> None:
     what a captured CUDA graph needs before each replay."""
 
     _, _, _, pos, nk = _batch_lists(st, b.widths)
-    need = max(-(-(st.lens[s] + wd) // LA.CHUNK) for s, wd in enumerate(b.widths))
+    need = max(LA.chunks_for(st.lens[s] + wd) for s, wd in enumerate(b.widths))
     if need > b.max_chunks:
         raise ValueError(f"context needs {need} key chunks, the batch was built for {b.max_chunks}")
     b.row_pos.copy_(torch.tensor(pos, dtype=torch.int32), non_blocking=True)
@@ -218,7 +218,7 @@ def make_batch(st: State, widths: Sequence[int], device, max_chunks: int | None 
     if rows > MAX_ROWS:
         raise ValueError(f"a forward takes at most {MAX_ROWS} packed rows, got {rows}")
     starts, seq, idx, pos, nk = _batch_lists(st, widths)
-    need = max(-(-(st.lens[s] + wd) // LA.CHUNK) for s, wd in enumerate(widths))
+    need = max(LA.chunks_for(st.lens[s] + wd) for s, wd in enumerate(widths))
     def i32(v):
         return torch.tensor(v, dtype=torch.int32).to(device, non_blocking=True)
     return Batch(widths, rows, i32(starts), i32(seq), i32(idx), i32(pos), i32(nk), max(widths), max(max_chunks or 0, need, 1))
@@ -278,10 +278,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
                  torch.empty((ng, R, c.v_heads), dtype=torch.float32, device=dev),
                  torch.empty((ng, R, 2 * kd + 2 * vd + 2 * c.v_heads), **bf),
                  torch.empty((na, R, c.kv_heads, c.head_dim), **bf), torch.empty((na, R, c.kv_heads, c.head_dim), **bf))
-    q_gdn = torch.empty((R, c.k_heads, c.dk), **bf)
-    y_gdn = torch.empty((R, c.v_heads, c.dv), **bf)
     q_att = torch.empty((R, c.heads, c.head_dim), **bf)
-    o_att = torch.empty((R, c.heads, c.head_dim), **bf)
     att_in = torch.empty((R, c.heads * 2 * c.head_dim + 2 * c.kv_heads * c.head_dim), **bf)
     mlp_in = torch.empty((R, 2 * c.intermediate), **bf) if c.experts == 0 else None
     moe_buf = None
@@ -292,48 +289,51 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
     scale = c.head_dim ** -0.5
 
-    def row_parallel(act, weight):
+    def row_parallel(act, weight, nxt):
         """(residual rows, gathered partials): one of the two is None."""
         if tp is None:
-            return lane_matmul(act, weight), None
-        return None, tp.gather_partials(lane_matmul(act, weight, f32=True))
+            return lane_matmul(act, weight, next_weight=nxt), None
+        return None, tp.gather_partials(lane_matmul(act, weight, f32=True, next_weight=nxt))
+
+    # each matmul tells the kernel which weight streams next, so that its first bytes wait in L2
+    def after(li):
+        return w.layers[li + 1].in_proj if li + 1 < len(w.layers) else (w.head if full_logits else None)
 
     x = lane_glue.embed(tokens.to(torch.int32), *w.embed, c.hidden, g)
     pending = parts = None
     gi = ai = 0
-    for layer in w.layers:
+    for li, layer in enumerate(w.layers):
         x, h = lane_glue.norm_xs(x, pending, layer.input_norm, c.eps, group=g, partials=parts)
         if layer.linear:
-            proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi])
+            proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi], next_weight=layer.out_proj)
             qkv, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
             bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + c.v_heads], proj[:, 2 * kd + 2 * vd + c.v_heads:]
-            lane_glue.gdn_pre(qkv, st.conv[gi], layer.conv, b.row_seq, b.row_idx, aa, bb, layer.A_log, layer.dt_bias,
-                              nk=c.k_heads, nv=c.v_heads, out=(q_gdn, rec.gdn_k[gi], rec.gdn_v[gi], rec.gdn_g[gi], rec.gdn_beta[gi]))
-            lane_gdn.gated_delta_chain(q_gdn, rec.gdn_k[gi], rec.gdn_v[gi], rec.gdn_g[gi], rec.gdn_beta[gi], st.rec[gi],
-                                       b.seq_start, out=y_gdn)
-            mixed = lane_glue.gdn_post(y_gdn, z, layer.norm, c.eps, group=g)
+            # conv + gates, recurrence and gated norm in one launch; k, v, g, beta land in the record for the commit
+            mixed = lane_gdn.gdn_mixer(qkv, z, aa, bb, st.conv[gi], layer.conv, layer.A_log, layer.dt_bias, layer.norm, st.rec[gi],
+                                       b.seq_start, nk=c.k_heads, nv=c.v_heads, eps=c.eps, group=g,
+                                       record=(rec.gdn_k[gi], rec.gdn_v[gi], rec.gdn_g[gi], rec.gdn_beta[gi]))
             gi += 1
         else:
-            proj = lane_matmul(h, layer.in_proj, out=att_in)
+            proj = lane_matmul(h, layer.in_proj, out=att_in, next_weight=layer.out_proj)
             nq = c.heads * 2 * c.head_dim
             nkv = c.kv_heads * c.head_dim
             lane_glue.attn_prep(proj[:, :nq], proj[:, nq:nq + nkv], proj[:, nq + nkv:], layer.q_norm, layer.k_norm, b.row_pos,
                                 w.inv_freq, c.eps, heads=c.heads, kv_heads=c.kv_heads, head_dim=c.head_dim,
                                 out=(q_att, rec.att_k[ai], rec.att_v[ai]))
+            mixed = new_packed(R, c.heads * c.head_dim, g, dev)
             LA.lane_attention(q_att, rec.att_k[ai], rec.att_v[ai], st.kv.k[ai], st.kv.v[ai], st.kv.table, st.seq_lens,
                               b.seq_start, b.row_nkeys, scale=scale, max_window=b.max_window, max_chunks=b.max_chunks,
-                              scratch=scratch, out=o_att)
-            mixed = lane_glue.gate_mul(o_att, proj[:, :nq], heads=c.heads, head_dim=c.head_dim, group=g)
+                              scratch=scratch, gate=proj[:, :nq], packed_out=mixed)      # output gate + packing in the merge
             ai += 1
-        r, rparts = row_parallel(mixed, layer.out_proj)
+        r, rparts = row_parallel(mixed, layer.out_proj, layer.gate_up if layer.experts is None else after(li))
         if layer.experts is not None:
             x, hrows = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts, rows_out=True, packed_out=False)
             pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf, ep), None
             continue
         x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts)
-        gu = lane_matmul(h, layer.gate_up, out=mlp_in)
+        gu = lane_matmul(h, layer.gate_up, out=mlp_in, next_weight=layer.down)
         act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)
-        pending, parts = row_parallel(act, layer.down)
+        pending, parts = row_parallel(act, layer.down, after(li))
     if not full_logits:
         _, hrows = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, rows_out=True, packed_out=False, partials=parts)
         return hrows, rec

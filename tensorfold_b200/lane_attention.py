@@ -13,7 +13,12 @@ import torch
 from . import _lib
 
 PAGE = 16
-CHUNK = 256
+
+
+def chunks_for(n_keys: int) -> int:
+    """Key chunks that hold positions 0..n_keys-1 (128 keys a chunk below 8192, 512 up to 65536, 2048 beyond)."""
+
+    return int(_lib.load().tf_attention_chunks(int(n_keys)))
 
 
 class PagedKV:
@@ -63,12 +68,15 @@ def scratch_bytes(rows: int, heads: int, head_dim: int, max_chunks: int) -> int:
 def lane_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    page_table: torch.Tensor, seq_lens: torch.Tensor, seq_start: torch.Tensor, row_nkeys: torch.Tensor, *,
                    scale: float, max_window: int, max_chunks: int, scratch: torch.Tensor | None = None,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, gate: torch.Tensor | None = None, packed_out=None) -> torch.Tensor:
     """Attend (R, H, D) queries to each row's sequence: committed pages, then the window rows up to its own.
 
     k_new, v_new (R, HK, D) window rows; k_pages, v_pages (pages, HK, 16, D); page_table (S, max_pages),
     seq_lens (S,), seq_start (S+1,), row_nkeys (R,) int32 on the device (row_nkeys = committed length +
-    place in window + 1). ``max_window`` bounds a sequence's rows, ``max_chunks`` the 256-key chunks.
+    place in window + 1). ``max_window`` bounds a sequence's rows, ``max_chunks`` the key chunks
+    (``chunks_for`` of the longest key count). ``gate``: the q projection's output rows ([q_h ; gate_h] per
+    head, a view with a row stride): the result is multiplied by sigmoid(gate_h). ``packed_out``: a
+    ``lane_qmm.Packed`` that receives the result as the output projection's input.
     """
 
     _lib.need_cuda(q, k_new, v_new, k_pages, v_pages, page_table, seq_lens, seq_start, row_nkeys)
@@ -89,15 +97,21 @@ def lane_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_
     need = scratch_bytes(r, h, d, max_chunks)
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
-    if out is None:
+    if out is None and packed_out is None:
         out = torch.empty_like(q)
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape != (r, h * 2 * d) or gate.stride(1) != 1):
+        raise ValueError("gate must be the (R, H * 2 * D) bf16 rows of the q projection")
+    if packed_out is not None and (packed_out.m != r or packed_out.k != h * d):
+        raise ValueError("packed_out must hold R rows of H * D inputs")
     with torch.cuda.device(q.device):
-        _lib.check(_lib.load().tf_lane_attention_paged(
+        _lib.check(_lib.load().tf_lane_attention_paged_gated(
             q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), page_table.data_ptr(),
-            page_table.shape[1], seq_lens.data_ptr(), seq_start.data_ptr(), row_nkeys.data_ptr(), out.data_ptr(),
-            scratch.data_ptr(), scratch.numel(), r, s, max_window, max_chunks, h, hk, d, float(scale), _lib.stream()),
-            "lane_attention")
-    return out
+            page_table.shape[1], seq_lens.data_ptr(), seq_start.data_ptr(), row_nkeys.data_ptr(), _lib.ptr(out),
+            _lib.ptr(gate), gate.stride(0) if gate is not None else 0,
+            packed_out.data.data_ptr() if packed_out is not None else None, packed_out.group if packed_out is not None else 64,
+            scratch.data_ptr(), scratch.numel(), r, s, max_window, max_chunks, h, hk, d, float(scale),
+            _lib.status(q.device).word.data_ptr(), _lib.stream()), "lane_attention")
+    return out if out is not None else packed_out
 
 
 def lane_sdpa(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, scale: float) -> torch.Tensor:
@@ -123,7 +137,7 @@ def lane_sdpa(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, s
     seq_start = torch.tensor([0, t], dtype=torch.int32, device=dev)
     nkeys = torch.arange(committed + 1, l + 1, dtype=torch.int32, device=dev)
     return lane_attention(queries.contiguous(), keys[committed:].contiguous(), values[committed:].contiguous(), kv.k[0], kv.v[0],
-                          kv.table, seq_lens, seq_start, nkeys, scale=scale, max_window=t, max_chunks=-(-l // CHUNK))
+                          kv.table, seq_lens, seq_start, nkeys, scale=scale, max_window=t, max_chunks=chunks_for(l))
 
 
 def kv_commit(k_new: torch.Tensor, v_new: torch.Tensor, kv: PagedKV, seq_lens: torch.Tensor, seq_start: torch.Tensor,
@@ -139,4 +153,4 @@ def kv_commit(k_new: torch.Tensor, v_new: torch.Tensor, kv: PagedKV, seq_lens: t
                    "kv_commit")
 
 
-__all__ = ["CHUNK", "PAGE", "PagedKV", "kv_commit", "lane_attention", "lane_sdpa", "scratch_bytes"]
+__all__ = ["PAGE", "chunks_for", "PagedKV", "kv_commit", "lane_attention", "lane_sdpa", "scratch_bytes"]

@@ -56,6 +56,44 @@ def gated_delta_chain(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torc
     return out
 
 
+def gdn_mixer(qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tensor, conv_state: torch.Tensor,
+              conv_weight: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor,
+              state: torch.Tensor, seq_start: torch.Tensor, *, nk: int, nv: int, eps: float, group: int = 64,
+              record: tuple, out=None, rows_out: bool = False):
+    """The GDN layer between its input and output projections in one launch: conv + gates
+    (``lane_glue.gdn_pre``), recurrence (``gated_delta_chain``) and gated norm (``lane_glue.gdn_post``),
+    with the bits of the three run one after the other (reference: the fused chain kernel of
+    ``families/qwen4_exp/cuda/gdn.cu:49-152``).
+
+    qkv (R, C), z (R, nv*128), a, b (R, nv): column views of the stacked projection's rows. ``record`` =
+    (k (R, nk, 128), v (R, nv, 128) bf16, g, beta (R, nv) fp32): what ``replay`` needs at commit. Returns
+    the packed rows for the output projection (and the plain rows with ``rows_out``)."""
+
+    from .lane_qmm import new_packed
+
+    _lib.need_cuda(qkv, z, a, b, conv_state, conv_weight, state, seq_start)
+    r, c = qkv.shape
+    s = state.shape[0]
+    k_rec, v_rec, g_rec, beta_rec = record
+    if (c != (2 * nk + nv) * 128 or z.shape != (r, nv * 128) or a.shape != (r, nv) or b.shape != (r, nv) or a.stride(0) != b.stride(0)
+            or qkv.stride(1) != 1 or z.stride(1) != 1 or conv_state.shape != (s, 3, c) or conv_weight.shape != (c, 4)
+            or state.shape != (s, nv, 128, 128) or state.dtype != torch.float32 or seq_start.shape != (s + 1,)
+            or k_rec.shape != (r, nk, 128) or v_rec.shape != (r, nv, 128) or g_rec.shape != (r, nv) or beta_rec.shape != (r, nv)):
+        raise ValueError("gdn_mixer: inconsistent shapes")
+    for t in (conv_state, conv_weight, state, k_rec, v_rec, g_rec, beta_rec):
+        if not t.is_contiguous():
+            raise ValueError("gdn_mixer: state, weights and record tensors must be contiguous")
+    packed = out if out is not None else new_packed(r, nv * 128, group, qkv.device)
+    rows = torch.empty((r, nv * 128), dtype=torch.bfloat16, device=qkv.device) if rows_out else None
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.load().tf_gdn_fused(
+            qkv.data_ptr(), qkv.stride(0), z.data_ptr(), z.stride(0), a.data_ptr(), b.data_ptr(), a.stride(0),
+            conv_state.data_ptr(), conv_weight.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), norm_weight.data_ptr(),
+            state.data_ptr(), k_rec.data_ptr(), v_rec.data_ptr(), g_rec.data_ptr(), beta_rec.data_ptr(), packed.data.data_ptr(),
+            _lib.ptr(rows), seq_start.data_ptr(), r, s, nk, nv, 128, 128, 4, group, float(eps), _lib.stream()), "gdn_mixer")
+    return (packed, rows) if rows_out else packed
+
+
 def gated_delta_tree(q, k, v, g, beta, state, parents) -> torch.Tensor:
     """Reference signature for one sequence: ``parents`` must describe a chain."""
 
@@ -103,4 +141,4 @@ def conv_commit(qkv: torch.Tensor, conv_state: torch.Tensor, seq_start: torch.Te
                    "conv_commit")
 
 
-__all__ = ["chain_parents", "conv_commit", "gated_delta_chain", "gated_delta_tree", "replay", "replay_path"]
+__all__ = ["chain_parents", "conv_commit", "gated_delta_chain", "gdn_mixer", "gated_delta_tree", "replay", "replay_path"]

@@ -188,12 +188,14 @@ def scratch_for(device: torch.device) -> torch.Tensor:
 
 
 def lane_matmul(x: torch.Tensor | Packed, weight: QWeight, *, f32: bool = False,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, next_weight: QWeight | None = None) -> torch.Tensor:
     """x (..., K) bf16 — or rows already ``Packed`` by the producing kernel — times the 4-bit
     ``weight`` (N, K) transposed -> (..., N) bf16.
 
     ``f32``: return the unrounded fp32 sums (a tensor-parallel rank's partial). More than
     ``MAX_ROWS`` rows run as several launches; a row's bits do not depend on which launch it rides in.
+    ``next_weight``: the weight of the matmul launched next on this stream; its first bytes are pulled
+    into L2 while this one finishes (a hint only).
     """
 
     lib = _lib.load()
@@ -226,9 +228,12 @@ def lane_matmul(x: torch.Tensor | Packed, weight: QWeight, *, f32: bool = False,
     with torch.cuda.device(dev):
         r0 = 0
         for c in chunks:
-            _lib.check(lib.tf_qmm(c.data.data_ptr(), weight.tiled.data_ptr(), out[r0:r0 + c.m].data_ptr(),
-                                  scratch.data_ptr(), scratch.numel(), c.m, weight.n, weight.k, weight.group,
-                                  1 if f32 else 0, st.word.data_ptr(), _lib.stream()), "lane_matmul")
+            nw = next_weight if c is chunks[-1] else weight
+            _lib.check(lib.tf_qmm_next(c.data.data_ptr(), weight.tiled.data_ptr(), out[r0:r0 + c.m].data_ptr(),
+                                       scratch.data_ptr(), scratch.numel(), c.m, weight.n, weight.k, weight.group,
+                                       1 if f32 else 0, nw.tiled.data_ptr() if nw is not None else None,
+                                       nw.n if nw is not None else 0, nw.k if nw is not None else 0,
+                                       nw.group if nw is not None else 0, st.word.data_ptr(), _lib.stream()), "lane_matmul")
             r0 += c.m
     return out.reshape(*lead, weight.n)
 

@@ -28,7 +28,9 @@ class LaneRunner:
                 st.kv.reserve(s, max_context + wd)     # pages for the whole run: the captured graph never reallocates
         st.kv.sync_table()
         st.sync_lens()
-        chunks = -(-(max_context + max(widths)) // 256)
+        from . import lane_attention as LA
+
+        chunks = LA.chunks_for(max_context + max(widths))
         self.batch: Batch = make_batch(st, widths, dev, max_chunks=chunks)
         self.rows = self.batch.rows
         self.tokens = torch.zeros(self.rows, dtype=torch.int32, device=dev)

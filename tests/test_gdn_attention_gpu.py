@@ -150,7 +150,7 @@ def test_lane_attention_ragged_windows(lib, d, h, hk):
     lens, widths = [0, 5, 509, 1030, 3], [3, 8, 8, 1, 16]
     kv, q, k_new, v_new, keys, vals, starts, nkeys = paged_setup(3, lens, widths, h, hk, d)
     seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
-    need = -(-(max(lens) + max(widths)) // LA.CHUNK)
+    need = LA.chunks_for(max(lens) + max(widths))
     args = dict(scale=d ** -0.5, max_window=max(widths), max_chunks=need)
     out = LA.lane_attention(q.cuda(), k_new.cuda(), v_new.cuda(), kv.k[0], kv.v[0], kv.table, seq_lens, starts.cuda(),
                             nkeys.cuda(), **args)
@@ -176,6 +176,56 @@ def test_lane_attention_ragged_windows(lib, d, h, hk):
     out2 = LA.lane_attention(q.cuda(), k_new.cuda(), v_new.cuda(), kv.k[0], kv.v[0], kv.table, seq_lens, starts.cuda(),
                              nkeys.cuda(), scale=d ** -0.5, max_window=max(widths), max_chunks=need + 4)
     assert_same_bits(out2, out, "chunk budget")
+
+
+def test_gated_attention_equals_attention_then_gate(lib):
+    """The merge kernel's fused output gate and packed output carry the bits of the two separate steps."""
+
+    from tensorfold_b200 import lane_attention as LA, lane_glue, lane_qmm
+
+    d, h, hk = 256, 24, 4
+    lens, widths = [300, 9000], [8, 5]
+    kv, q, k_new, v_new, keys, vals, starts, nkeys = paged_setup(11, lens, widths, h, hk, d)
+    seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    need = LA.chunks_for(max(l + w for l, w in zip(lens, widths)))
+    r = sum(widths)
+    qg = torch.randn((r, h * 2 * d + 64), generator=torch.Generator().manual_seed(5)).to(BF).cuda()[:, :h * 2 * d]
+    args = (q.cuda(), k_new.cuda(), v_new.cuda(), kv.k[0], kv.v[0], kv.table, seq_lens, starts.cuda(), nkeys.cuda())
+    kw = dict(scale=d ** -0.5, max_window=max(widths), max_chunks=need)
+    plain = LA.lane_attention(*args, **kw)
+    want_packed, want_rows = lane_glue.gate_mul(plain, qg, heads=h, head_dim=d, group=64, rows_out=True)
+    rows = torch.empty_like(plain)
+    packed = lane_qmm.new_packed(r, h * d, 64, "cuda")
+    packed.data.fill_(7)
+    LA.lane_attention(*args, out=rows, gate=qg, packed_out=packed, **kw)
+    assert_same_bits(rows.reshape(r, -1), want_rows, "gated rows")
+    assert torch.equal(packed.data, want_packed.data), "packed output of the fused merge"
+    r0 = 0
+    for i, wd in enumerate(widths):
+        want = O.attention(q[r0:r0 + wd], keys[i], vals[i], nkeys[r0:r0 + wd], d ** -0.5)
+        assert_close(plain[r0:r0 + wd], want, f"seq {i}", rel=2e-2, abs_=1e-2)
+        r0 += wd
+
+
+@pytest.mark.parametrize("ctx", [4096, 20000, 32768])
+def test_lane_attention_long_context(lib, ctx):
+    """Config-3 attention shape (24 query / 4 KV heads of 256) at the benchmarked context lengths and at the
+    reference's own long case (20000 keys, tests/test_lane_attention.py:25-49): W = 8 window rows against the
+    fp32 oracle, and the last row alone (serial form) bit-equal to the same row inside the window."""
+
+    from tensorfold_b200 import lane_attention as LA
+
+    d, h, hk, w = 256, 24, 4, 8
+    gen = torch.Generator().manual_seed(ctx)
+    keys = torch.randn((ctx + w, hk, d), generator=gen).to(BF)
+    vals = torch.randn((ctx + w, hk, d), generator=gen).to(BF)
+    q = torch.randn((w, h, d), generator=gen).to(BF)
+    out = LA.lane_sdpa(q.cuda(), keys.cuda(), vals.cuda(), d ** -0.5)
+    nkeys = torch.arange(ctx + 1, ctx + w + 1)
+    want = O.attention(q, keys, vals, nkeys, d ** -0.5)
+    assert_close(out, want, f"context {ctx}", rel=2e-2, abs_=1e-2)
+    one = LA.lane_sdpa(q[w - 1:].cuda(), keys.cuda(), vals.cuda(), d ** -0.5)
+    assert_same_bits(one, out[w - 1:], "last row alone == last row of the window")
 
 
 def test_lane_sdpa_reference_shape_and_kv_commit(lib):
@@ -256,3 +306,83 @@ def test_keyed_sampling_matches_reference_fixture(lib):
         assert alone == got[7:8]
     greedy = S.sample_rows(logits, positions.tolist(), None).cpu().numpy()
     assert np.array_equal(greedy, np.array(O.sample_rows(logits.float().cpu().numpy(), positions, None)))
+
+
+def _mixer_inputs(seed, widths, nk, nv):
+    gen = torch.Generator().manual_seed(seed)
+    r, s = sum(widths), len(widths)
+    c = (2 * nk + nv) * 128
+    proj = torch.randn((r, c + nv * 128 + 2 * nv), generator=gen).to(BF)          # [qkv | z | b | a] rows of the stacked projection
+    conv_state = torch.randn((s, 3, c), generator=gen).to(BF)
+    conv_w = (0.3 * torch.randn((c, 4), generator=gen)).to(BF)
+    a_log, dt_bias = 0.5 * torch.randn(nv, generator=gen), 0.5 * torch.randn(nv, generator=gen)
+    norm_w = (1 + 0.05 * torch.randn(128, generator=gen)).to(BF)
+    state = 0.1 * torch.randn((s, nv, 128, 128), generator=gen)
+    starts = torch.tensor([0] + list(np.cumsum(widths)), dtype=torch.int32)
+    row_seq = torch.tensor([i for i, w in enumerate(widths) for _ in range(w)], dtype=torch.int32)
+    row_idx = torch.tensor([t for w in widths for t in range(w)], dtype=torch.int32)
+    return proj, conv_state, conv_w, a_log, dt_bias, norm_w, state, starts, row_seq, row_idx
+
+
+@pytest.mark.parametrize("widths,nk,nv,group", [([8, 3, 1, 13], 2, 4, 64), ([5, 8], 2, 4, 32), ([8] * 16, 16, 32, 64)])
+def test_gdn_mixer_in_one_launch_has_the_bits_of_the_three_kernels(lib, widths, nk, nv, group):
+    """Conv + gates, recurrence and gated norm fused (tf_gdn_fused) against gdn_pre -> gated_delta_chain ->
+    gdn_post; the last case has the head counts of the benchmark's gated-DeltaNet layers (16 key / 32 value
+    heads of 128) at the 128 rows one forward takes, also checked against the fp32 oracle recurrence."""
+
+    from tensorfold_b200 import lane_gdn, lane_glue
+
+    proj, conv_state, conv_w, a_log, dt_bias, norm_w, state, starts, row_seq, row_idx = _mixer_inputs(len(widths), widths, nk, nv)
+    r, c = sum(widths), (2 * nk + nv) * 128
+    d = lambda t: t.cuda()
+    projc = d(proj)
+    qkv, z = projc[:, :c], projc[:, c:c + nv * 128]
+    bb, aa = projc[:, c + nv * 128:c + nv * 128 + nv], projc[:, c + nv * 128 + nv:]
+    q, k, v, g, beta = lane_glue.gdn_pre(qkv, d(conv_state), d(conv_w), d(row_seq), d(row_idx), aa, bb, d(a_log), d(dt_bias), nk=nk, nv=nv)
+    y = lane_gdn.gated_delta_chain(q, k, v, g, beta, d(state), d(starts))
+    want_packed, want_rows = lane_glue.gdn_post(y, z, d(norm_w), 1e-6, group=group, rows_out=True)
+    rec = (torch.empty_like(k), torch.empty_like(v), torch.empty_like(g), torch.empty_like(beta))
+    packed, rows = lane_gdn.gdn_mixer(qkv, z, aa, bb, d(conv_state), d(conv_w), d(a_log), d(dt_bias), d(norm_w), d(state), d(starts),
+                                      nk=nk, nv=nv, eps=1e-6, group=group, record=rec, rows_out=True)
+    assert_same_bits(rows, want_rows, "mixer rows")
+    assert torch.equal(packed.data, want_packed.data), "mixer packed output"
+    for got, want, name in zip(rec, (k, v, g, beta), ("k", "v", "g", "beta")):
+        assert torch.equal(got.view(torch.int32) if got.dtype == torch.float32 else got.view(torch.int16),
+                           want.view(torch.int32) if want.dtype == torch.float32 else want.view(torch.int16)), f"record {name}"
+    if len(widths) == 16:
+        # the recurrence at this shape against the fp32 oracle (tolerance of tests/cuda/test_flashnext_kernels.py:216-218)
+        for s in (0, 7, 15):
+            r0 = int(starts[s])
+            sl = slice(r0, r0 + widths[s])
+            y_ref, _ = O.gdn_recurrence(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), g[sl].cpu(), beta[sl].cpu(), state[s])
+            err = (y[sl].float().cpu() - y_ref.float()).abs().max()
+            assert err < 0.05 * y_ref.float().abs().max()
+
+
+def test_gdn_lane_step_at_config_2_shape(lib):
+    """The gated-DeltaNet lane step as the benchmark configs give it: 32 sequences x 8 rows, 16 key / 32 value
+    heads of 128, fp32 state [32, 32, 128, 128] ~ N(0, 0.1): the 8-row window against the fp32 oracle, and its
+    rows bit-equal to 8 one-row steps with the state replayed in between (replay(keep) == state after keep steps)."""
+
+    from tensorfold_b200 import lane_gdn
+
+    widths = [8] * 32
+    q, k, v, g, beta, state, starts = gdn_inputs(2, widths, hk=16, hv=32)
+    dev = [t.cuda() for t in (q, k, v, g, beta, state, starts)]
+    y = lane_gdn.gated_delta_chain(*dev)
+    for s in (0, 13, 31):
+        sl = slice(8 * s, 8 * s + 8)
+        y_ref, _ = O.gdn_recurrence(q[sl], k[sl], v[sl], g[sl], beta[sl], state[s])
+        assert (y[sl].float().cpu() - y_ref.float()).abs().max() < 0.05 * y_ref.float().abs().max()
+    st = dev[5].clone()
+    one = torch.ones(32, dtype=torch.int32).cuda()
+    ss = torch.arange(33, dtype=torch.int32).cuda()
+    for t in range(8):
+        sel = (torch.arange(32) * 8 + t).cuda()
+        ys = lane_gdn.gated_delta_chain(dev[0][sel].contiguous(), dev[1][sel].contiguous(), dev[2][sel].contiguous(),
+                                        dev[3][sel].contiguous(), dev[4][sel].contiguous(), st, ss)
+        assert_same_bits(ys, y[sel], f"row {t}: window == serial")
+        lane_gdn.replay(dev[1][sel].contiguous(), dev[2][sel].contiguous(), dev[3][sel].contiguous(), dev[4][sel].contiguous(), st, ss, one)
+    full = dev[5].clone()
+    lane_gdn.replay(dev[1], dev[2], dev[3], dev[4], full, dev[6], torch.full((32,), 8, dtype=torch.int32).cuda())
+    assert torch.equal(full.view(torch.int32), st.view(torch.int32)), "replay(8) == eight serial steps"

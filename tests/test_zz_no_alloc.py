@@ -37,7 +37,9 @@ def _case(seed, lens, widths, h, hk, d):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
     starts = i32([0] + list(np.cumsum(widths)))
     nkeys = i32([lens[i] + t + 1 for i in range(s) for t in range(widths[i])])
-    chunks = max(-(-(l + w) // 256) for l, w in zip(lens, widths))
+    from tensorfold_b200 import lane_attention as LA
+
+    chunks = max(LA.chunks_for(l + w) for l, w in zip(lens, widths))
     return kv, q, k_new, v_new, i32(lens), starts, nkeys, r, s, max(widths), chunks
 
 
