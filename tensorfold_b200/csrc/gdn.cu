@@ -3,7 +3,7 @@
 // Per (sequence, value head, value row) the fp32 state row S[0..127] (key dimension) stays in
 // registers across the window's rows, split over 4 lanes of 32 values each:
 //     S    <- S * g
-//     mem   = S . k                      (fp32, 32 sequential fma per lane, then a 4-lane xor tree)
+//     mem   = S . k                      (fp32: per lane four 8-term fma chains combined pairwise, then a 4-lane xor tree)
 //     delta = (v - mem) * beta
 //     S    <- S + k * delta              (fma)
 //     y     = S . q
@@ -22,6 +22,52 @@ namespace {
 constexpr int kDk = 128;            // key head dim (state row length)
 constexpr int kRowsPerCta = 32;     // value rows per CTA: 4 lanes each -> 128 threads
 constexpr int kTile = 8;            // window rows staged per pass
+
+// One window row applied to the 32 state values a lane holds (key elements 16*i + 4*j + e of one value row),
+// the same statements in the chain, replay and fused kernels: four partial dot products per lane (one per
+// element of the float4s, eight terms each, so the fma chains are short), combined pairwise, then the
+// 4-lane xor tree.
+template <bool OUT>
+__device__ __forceinline__ float gdn_row_step(float4 (&s)[8], const float* krow, const float* qrow, int j, float decay, float vval,
+                                              float beta) {
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 kv = *reinterpret_cast<const float4*>(krow + i * 16 + j * 4);
+        s[i].x *= decay; s[i].y *= decay; s[i].z *= decay; s[i].w *= decay;
+        m0 = __fmaf_rn(s[i].x, kv.x, m0);
+        m1 = __fmaf_rn(s[i].y, kv.y, m1);
+        m2 = __fmaf_rn(s[i].z, kv.z, m2);
+        m3 = __fmaf_rn(s[i].w, kv.w, m3);
+    }
+    float mem = (m0 + m1) + (m2 + m3);
+    mem += __shfl_xor_sync(0xffffffffu, mem, 1);
+    mem += __shfl_xor_sync(0xffffffffu, mem, 2);
+    const float delta = (vval - mem) * beta;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 kv = *reinterpret_cast<const float4*>(krow + i * 16 + j * 4);
+        s[i].x = __fmaf_rn(kv.x, delta, s[i].x);
+        s[i].y = __fmaf_rn(kv.y, delta, s[i].y);
+        s[i].z = __fmaf_rn(kv.z, delta, s[i].z);
+        s[i].w = __fmaf_rn(kv.w, delta, s[i].w);
+        if (OUT) {
+            const float4 qv = *reinterpret_cast<const float4*>(qrow + i * 16 + j * 4);
+            o0 = __fmaf_rn(s[i].x, qv.x, o0);
+            o1 = __fmaf_rn(s[i].y, qv.y, o1);
+            o2 = __fmaf_rn(s[i].z, qv.z, o2);
+            o3 = __fmaf_rn(s[i].w, qv.w, o3);
+        }
+    }
+    float out = 0.f;
+    if (OUT) {
+        out = (o0 + o1) + (o2 + o3);
+        out += __shfl_xor_sync(0xffffffffu, out, 1);
+        out += __shfl_xor_sync(0xffffffffu, out, 2);
+    }
+    return out;
+}
 
 struct GdnArgs {
     const __nv_bfloat16* q;         // [R, KH, 128]   (unused by replay)
@@ -110,41 +156,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 4) gdn_kernel(const GdnArgs a) {
         __syncthreads();
         if (!live) continue;
         for (int r = 0; r < rows; ++r) {
-            const float decay = gs[r];
-            float mem = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
-                s[i].x *= decay; s[i].y *= decay; s[i].z *= decay; s[i].w *= decay;
-                mem = __fmaf_rn(s[i].x, kv.x, mem);
-                mem = __fmaf_rn(s[i].y, kv.y, mem);
-                mem = __fmaf_rn(s[i].z, kv.z, mem);
-                mem = __fmaf_rn(s[i].w, kv.w, mem);
-            }
-            mem += __shfl_xor_sync(0xffffffffu, mem, 1);
-            mem += __shfl_xor_sync(0xffffffffu, mem, 2);
-            const float delta = (vs[r][lr] - mem) * bs[r];
-            float out = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
-                s[i].x = __fmaf_rn(kv.x, delta, s[i].x);
-                s[i].y = __fmaf_rn(kv.y, delta, s[i].y);
-                s[i].z = __fmaf_rn(kv.z, delta, s[i].z);
-                s[i].w = __fmaf_rn(kv.w, delta, s[i].w);
-                if (OUT) {
-                    const float4 qv = *reinterpret_cast<const float4*>(&qs[r][i * 16 + j * 4]);
-                    out = __fmaf_rn(s[i].x, qv.x, out);
-                    out = __fmaf_rn(s[i].y, qv.y, out);
-                    out = __fmaf_rn(s[i].z, qv.z, out);
-                    out = __fmaf_rn(s[i].w, qv.w, out);
-                }
-            }
-            if (OUT) {
-                out += __shfl_xor_sync(0xffffffffu, out, 1);
-                out += __shfl_xor_sync(0xffffffffu, out, 2);
-                if (j == 0) a.y[((size_t)(r0 + t0 + r) * a.VH + head) * a.DV + dvrow] = f2bf(out);
-            }
+            const float out = gdn_row_step<OUT>(s, ks[r], qs[OUT ? r : 0], j, gs[r], vs[r][lr], bs[r]);
+            if (OUT && j == 0) a.y[((size_t)(r0 + t0 + r) * a.VH + head) * a.DV + dvrow] = f2bf(out);
         }
     }
     if (live && a.state_out != nullptr) {
@@ -207,97 +220,103 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(const GdnFusedArgs a) {
     for (int t0 = 0; t0 < n; t0 += kTile) {
         const int rows = min(kTile, n - t0);
         __syncthreads();
-        // ---- 1. conv + gates: task = (row of the pass, part) with part 0 = q, 1 = k, 2 = v ----
-        for (int task = warp; task < rows * 3; task += 16) {
-            const int r = task / 3, part = task - 3 * r;
-            const int row = r0 + t0 + r, idx = t0 + r;             // idx: the row's place in its sequence's chain
-            const int chead = part == 0 ? kh : part == 1 ? a.KH + kh : 2 * a.KH + head;
-            const int ch0 = chead * 128 + lane * 4;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            float wt[16];
-            {
-                const uint4* wp = reinterpret_cast<const uint4*>(a.conv_w + (size_t)ch0 * 4);
-                float lo[8], hi[8];
-                unpack8(wp[0], lo);
-                unpack8(wp[1], hi);
+        // ---- 1. conv + gates: warps 0..7 take q and k of row `warp`, warps 8..15 v and the gates of row
+        //         `warp - 8`; a warp's loads are all issued before the first use, so the pass costs one trip ----
+        {
+            const int r = warp & 7;
+            if (r < rows) {
+                const int row = r0 + t0 + r, idx = t0 + r;         // idx: the row's place in its sequence's chain
+                constexpr int NP = 2;
+                const int nparts = warp < 8 ? 2 : 1;
+                uint4 wq[NP][2];
+                uint2 xv[NP][4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { wt[i] = lo[i]; wt[8 + i] = hi[i]; }
-            }
+                for (int pi = 0; pi < NP; ++pi) {
+                    if (pi < nparts) {
+                        const int part = warp < 8 ? pi : 2;
+                        const int chead = part == 0 ? kh : part == 1 ? a.KH + kh : 2 * a.KH + head;
+                        const int ch0 = chead * 128 + lane * 4;
+                        const uint4* wp = reinterpret_cast<const uint4*>(a.conv_w + (size_t)ch0 * 4);
+                        wq[pi][0] = wp[0]; wq[pi][1] = wp[1];
 #pragma unroll
-            for (int tap = 0; tap < 4; ++tap) {
-                const int src = idx + tap;                         // index into [conv_state (3 rows); window rows]
-                const __nv_bfloat16* p = src < 3 ? a.conv_state + ((size_t)seq * 3 + src) * C + ch0
-                                                 : a.qkv + (size_t)(row - idx + src - 3) * a.qkv_stride + ch0;
-                const uint2 xv = *reinterpret_cast<const uint2*>(p);
-                const float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
+                        for (int tap = 0; tap < 4; ++tap) {
+                            const int src = idx + tap;             // index into [conv_state (3 rows); window rows]
+                            const __nv_bfloat16* p = src < 3 ? a.conv_state + ((size_t)seq * 3 + src) * C + ch0
+                                                             : a.qkv + (size_t)(row - idx + src - 3) * a.qkv_stride + ch0;
+                            xv[pi][tap] = *reinterpret_cast<const uint2*>(p);
+                        }
+                    }
+                }
+                float av = 0.f, bv = 0.f;
+                if (warp >= 8 && lane == 0) {
+                    av = bf2f(a.a_in[(size_t)row * a.ab_stride + head]);
+                    bv = bf2f(a.b_in[(size_t)row * a.ab_stride + head]);
+                }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[i] = __fmaf_rn(xf[i], wt[i * 4 + tap], acc[i]);
-            }
-            float c[4];
+                for (int pi = 0; pi < NP; ++pi) {
+                    if (pi < nparts) {
+                        const int part = warp < 8 ? pi : 2;
+                        float wt[16];
+                        {
+                            float lo[8], hi[8];
+                            unpack8(wq[pi][0], lo);
+                            unpack8(wq[pi][1], hi);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[i] = round_bf16(acc[i] * sigmoidf_(acc[i]));
-            if (part < 2) {
-                float ss = 0.f;
+                            for (int i = 0; i < 8; ++i) { wt[i] = lo[i]; wt[8 + i] = hi[i]; }
+                        }
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) ss += c[i] * c[i];
-                const float inv = 1.0f / sqrtf(warp_sum(ss) / 128.0f + 1e-6f);
-                const float scale = part == 0 ? 1.0f / 128.0f : 0.08838834764831845f;   // 1/dk, dk^-1/2
-                const uint2 packed = make_uint2(pack_bf16(c[0] * inv * scale, c[1] * inv * scale),
-                                                pack_bf16(c[2] * inv * scale, c[3] * inv * scale));
-                float* dst = (part == 0 ? qs[r] : ks[r]) + lane * 4;
-                dst[0] = bf16_lo(packed.x); dst[1] = bf16_hi(packed.x); dst[2] = bf16_lo(packed.y); dst[3] = bf16_hi(packed.y);
-                // one of the value heads that share this key head keeps k for the commit
-                if (part == 1 && head % (a.VH / a.KH) == 0)
-                    *reinterpret_cast<uint2*>(a.k_out + ((size_t)row * a.KH + kh) * 128 + lane * 4) = packed;
-            } else {
-                const uint2 packed = make_uint2(pack_bf16(c[0], c[1]), pack_bf16(c[2], c[3]));
-                float* dst = vs[r] + lane * 4;
-                dst[0] = c[0]; dst[1] = c[1]; dst[2] = c[2]; dst[3] = c[3];
-                *reinterpret_cast<uint2*>(a.v_out + ((size_t)row * a.VH + head) * 128 + lane * 4) = packed;
-                if (lane == 0) {
-                    const float av = bf2f(a.a_in[(size_t)row * a.ab_stride + head]) + a.dt_bias[head];
-                    const float sp = av > 20.0f ? av : logf(1.0f + expf(av));
-                    const float gv = expf(-expf(a.a_log[head]) * sp);
-                    const float bv = sigmoidf_(bf2f(a.b_in[(size_t)row * a.ab_stride + head]));
-                    gs[r] = gv; bs[r] = bv;
-                    a.g_out[(size_t)row * a.VH + head] = gv;
-                    a.beta_out[(size_t)row * a.VH + head] = bv;
+                        for (int tap = 0; tap < 4; ++tap) {
+                            const float xf[4] = {bf16_lo(xv[pi][tap].x), bf16_hi(xv[pi][tap].x), bf16_lo(xv[pi][tap].y), bf16_hi(xv[pi][tap].y)};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[i] = __fmaf_rn(xf[i], wt[i * 4 + tap], acc[i]);
+                        }
+                        float c[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) c[i] = round_bf16(acc[i] * sigmoidf_(acc[i]));
+                        if (part < 2) {
+                            float ss = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) ss += c[i] * c[i];
+                            const float inv = 1.0f / sqrtf(warp_sum(ss) / 128.0f + 1e-6f);
+                            const float scale = part == 0 ? 1.0f / 128.0f : 0.08838834764831845f;   // 1/dk, dk^-1/2
+                            const uint2 packed = make_uint2(pack_bf16(c[0] * inv * scale, c[1] * inv * scale),
+                                                            pack_bf16(c[2] * inv * scale, c[3] * inv * scale));
+                            float* dst = (part == 0 ? qs[r] : ks[r]) + lane * 4;
+                            dst[0] = bf16_lo(packed.x); dst[1] = bf16_hi(packed.x); dst[2] = bf16_lo(packed.y); dst[3] = bf16_hi(packed.y);
+                            // one of the value heads that share this key head keeps k for the commit
+                            if (part == 1 && head % (a.VH / a.KH) == 0)
+                                *reinterpret_cast<uint2*>(a.k_out + ((size_t)row * a.KH + kh) * 128 + lane * 4) = packed;
+                        } else {
+                            const uint2 packed = make_uint2(pack_bf16(c[0], c[1]), pack_bf16(c[2], c[3]));
+                            float* dst = vs[r] + lane * 4;
+                            dst[0] = c[0]; dst[1] = c[1]; dst[2] = c[2]; dst[3] = c[3];
+                            *reinterpret_cast<uint2*>(a.v_out + ((size_t)row * a.VH + head) * 128 + lane * 4) = packed;
+                            if (lane == 0) {
+                                const float ag = av + a.dt_bias[head];
+                                const float sp = ag > 20.0f ? ag : logf(1.0f + expf(ag));
+                                const float gv = expf(-expf(a.a_log[head]) * sp);
+                                const float bvv = sigmoidf_(bv);
+                                gs[r] = gv; bs[r] = bvv;
+                                a.g_out[(size_t)row * a.VH + head] = gv;
+                                a.beta_out[(size_t)row * a.VH + head] = bvv;
+                            }
+                        }
+                    }
                 }
             }
+        }
+        // the gated norm's z and weight, fetched now so that the trip hides behind the recurrence
+        uint4 z_pre = make_uint4(0, 0, 0, 0), w_pre = make_uint4(0, 0, 0, 0);
+        if (warp * 2 + (lane >> 4) < rows) {
+            const int row = r0 + t0 + warp * 2 + (lane >> 4), l16 = lane & 15;
+            z_pre = *reinterpret_cast<const uint4*>(a.z + (size_t)row * a.z_stride + head * 128 + 8 * l16);
+            w_pre = reinterpret_cast<const uint4*>(a.norm_w)[l16];
         }
         __syncthreads();
         // ---- 2. recurrence over the pass's rows ----
         for (int r = 0; r < rows; ++r) {
-            const float decay = gs[r];
-            float mem = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
-                s[i].x *= decay; s[i].y *= decay; s[i].z *= decay; s[i].w *= decay;
-                mem = __fmaf_rn(s[i].x, kv.x, mem);
-                mem = __fmaf_rn(s[i].y, kv.y, mem);
-                mem = __fmaf_rn(s[i].z, kv.z, mem);
-                mem = __fmaf_rn(s[i].w, kv.w, mem);
-            }
-            mem += __shfl_xor_sync(0xffffffffu, mem, 1);
-            mem += __shfl_xor_sync(0xffffffffu, mem, 2);
-            const float delta = (vs[r][dvrow] - mem) * bs[r];
-            float out = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 kv = *reinterpret_cast<const float4*>(&ks[r][i * 16 + j * 4]);
-                const float4 qv = *reinterpret_cast<const float4*>(&qs[r][i * 16 + j * 4]);
-                s[i].x = __fmaf_rn(kv.x, delta, s[i].x);
-                s[i].y = __fmaf_rn(kv.y, delta, s[i].y);
-                s[i].z = __fmaf_rn(kv.z, delta, s[i].z);
-                s[i].w = __fmaf_rn(kv.w, delta, s[i].w);
-                out = __fmaf_rn(s[i].x, qv.x, out);
-                out = __fmaf_rn(s[i].y, qv.y, out);
-                out = __fmaf_rn(s[i].z, qv.z, out);
-                out = __fmaf_rn(s[i].w, qv.w, out);
-            }
-            out += __shfl_xor_sync(0xffffffffu, out, 1);
-            out += __shfl_xor_sync(0xffffffffu, out, 2);
+            const float out = gdn_row_step<true>(s, ks[r], qs[r], j, gs[r], vs[r][dvrow], bs[r]);
             if (j == 0) ys[r][dvrow] = round_bf16(out);
         }
         __syncthreads();
@@ -312,8 +331,8 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(const GdnFusedArgs a) {
             if (live) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) yv[i] = ys[r][l16 * 8 + i];
-                unpack8(*reinterpret_cast<const uint4*>(a.z + (size_t)row * a.z_stride + head * 128 + 8 * l16), zv);
-                unpack8(reinterpret_cast<const uint4*>(a.norm_w)[l16], wv);
+                unpack8(z_pre, zv);
+                unpack8(w_pre, wv);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) ss += yv[i] * yv[i];
             }

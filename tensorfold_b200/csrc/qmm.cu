@@ -40,8 +40,14 @@ namespace tf {
 namespace {
 
 constexpr int kWorkers = 148;
-constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every row bucket, so that the
-                                // K segments (hence the bits) do not depend on the row count
+// k tiles per schedule item: a function of the weight's shape only, the same for every row bucket, so that
+// the K segments (hence the bits) do not depend on the row count. One tile keeps the workers' shares within
+// a tile of each other; a narrow weight (fewer than 18 column blocks) would then be cut into dozens of
+// segments a block, so its blocks are cut into eight items instead.
+constexpr int kMaxCutsNarrow = 8;
+__host__ __device__ inline int item_tiles_for(int CB, int KT) {
+    return CB * kMaxCutsNarrow < kWorkers ? (KT + kMaxCutsNarrow - 1) / kMaxCutsNarrow : 1;
+}
 constexpr int kWarps = 16;      // column tiles per column block (baked into the layout)
 constexpr int kCols = kWarps * 16;
 
@@ -71,7 +77,6 @@ struct Cfg {
     static constexpr int STAGES = BUDGET / (STAGE_BYTES + 16) > 12 ? 12 : BUDGET / (STAGE_BYTES + 16);
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
     static_assert(STAGES >= 2, "the ring needs at least two stages");
-    static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
 };
 
 // Optional per-CTA timeline for profiling: when set (tf_qmm_set_trace), each launch writes eight
@@ -115,7 +120,7 @@ struct Args {
     long long w_stride, xp_stride, y_stride;
 };
 
-// Work items (column block, group of kItemTiles k tiles) are split evenly over kWorkers CTAs.
+// Work items (column block, group of item_tiles_for k tiles) are split evenly over kWorkers CTAs.
 // cta * total stays below 2^31: the entry points refuse shapes with more than 2^30 / kWorkers items
 __host__ __device__ inline int range_begin(int cta, int total) { return (int)((unsigned)cta * (unsigned)total / (unsigned)kWorkers); }
 
@@ -144,9 +149,7 @@ __device__ __forceinline__ float4 ld_volatile16(const float4* p) {
 // adds them in worker order, which is k order, and writes the output. No tickets, flags or fences, one
 // round trip on the critical path, and nothing to reset. The launch number is the worker's own counter in scratch, advanced once
 // per launch before dependents may start, so every worker of a launch holds the same number.
-// FULL: K is a whole number of pipeline stages, so every stage holds KTS k tiles and the loop over them
-// carries no test (the compiler then interleaves the tiles' instruction streams).
-template <class C, bool MULTI, bool FULL>
+template <class C, bool MULTI>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) {
     constexpr int MB = C::MB, KTS = C::KTS, STAGES = C::STAGES, CW = C::CW, T = C::T, NC = CW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
     constexpr bool multi = MULTI;      // the grouped form is its own instantiation: the plain one pays nothing for it
     // Grouped launches never cut a column block along K: where the cut falls would depend on how many
     // problems the launch holds, that is on the other rows' routing. One item = a whole (problem, block).
-    const int item_tiles = multi ? ((KT + KTS - 1) / KTS) * KTS : kItemTiles;   // a constant in the plain form
+    const int item_tiles = multi ? ((KT + KTS - 1) / KTS) * KTS : item_tiles_for(CB, KT);
     const int SPB = (KT + item_tiles - 1) / item_tiles;   // schedule items per column block
     if (multi) pdl_wait();                                // the problem list is the previous kernel's output
     const int probs = multi ? min(*a.prob_count, a.max_probs) : 1;
@@ -229,13 +232,13 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             stamp(tr, 7);
             if (a.next_w != nullptr) {
                 // where this worker's range of the next matmul starts (its items are cut like this one's)
-                const int nKT = a.next_K >> 6, nCB = (a.next_N + kCols - 1) / kCols, nSPB = (nKT + kItemTiles - 1) / kItemTiles;
+                const int nKT = a.next_K >> 6, nCB = (a.next_N + kCols - 1) / kCols, nIT = item_tiles_for(nCB, nKT), nSPB = (nKT + nIT - 1) / nIT;
                 const int ntotal = nCB * nSPB;
                 const int nb = range_begin(blockIdx.x, ntotal), ne = range_begin(blockIdx.x + 1, ntotal);
                 const size_t tile_bytes = (size_t)kWarps * rec_bytes(a.next_group);      // one k tile of a column block
-                const size_t at = ((size_t)(nb / nSPB) * nKT + (size_t)(nb % nSPB) * kItemTiles) * tile_bytes;
+                const size_t at = ((size_t)(nb / nSPB) * nKT + (size_t)(nb % nSPB) * nIT) * tile_bytes;
                 const size_t whole = (size_t)nCB * nKT * tile_bytes;
-                size_t len = (size_t)(ne - nb) * kItemTiles * tile_bytes;
+                size_t len = (size_t)(ne - nb) * nIT * tile_bytes;
                 if (len > (size_t)a.prefetch_bytes) len = (size_t)a.prefetch_bytes;
                 if (at + len > whole) len = whole > at ? whole - at : 0;
                 for (size_t off = 0; off < len; off += 32768) {
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             const uint8_t* xst = sb + C::W_BYTES;
 #pragma unroll
             for (int kt = 0; kt < KTS; ++kt) {
-                if (FULL || kt < nkt) {
+                if (kt < nkt) {
                     const uint8_t* xt = xst + kt * C::XTILE;
                     const float* xsums = reinterpret_cast<const float*>(xt + C::ROWS * 128) + 2 * t;
                     uint32_t af[T][4][4];
@@ -365,7 +368,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             int o = blockIdx.x + 1;
             bool more = true;
             while (more) {
-                constexpr int SB = 4;
+                constexpr int SB = MB <= 2 ? 4 : 1;              // segments fetched together
+                constexpr int UN = T * MB, UB = UN >= 4 ? 4 : UN;  // accumulator units (4 values each), units per fetch
                 int who[SB], cnt = 0;
                 for (; o < kWorkers && cnt < SB; ++o) {
                     const int ob = range_begin(o, total);
@@ -375,40 +379,40 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
                 }
                 if (o >= kWorkers) more = false;
                 if (cnt == 0) break;
-                // fetch every packet of the batch; a packet that does not carry this launch's number yet is
-                // fetched again (bounded)
-                float4 v[SB][T][MB][2];
-                bool ready = false;
-                for (int spin = 0; spin < (1 << 20) && !ready; ++spin) {
-                    ready = true;
+#pragma unroll
+                for (int u0 = 0; u0 < UN; u0 += UB) {
+                    // fetch the packets of these units from every segment of the batch; a packet that does not
+                    // carry this launch's number yet is fetched again (bounded)
+                    float4 v[SB][UB][2];
+                    bool ready = false;
+                    for (int spin = 0; spin < (1 << 20) && !ready; ++spin) {
+                        ready = true;
+#pragma unroll
+                        for (int j = 0; j < SB; ++j)
+                            if (j < cnt) {
+                                const float4* slot = reinterpret_cast<const float4*>(a.slots + (size_t)who[j] * (2 * kSlotFloats));
+#pragma unroll
+                                for (int u = 0; u < UB; ++u)
+#pragma unroll
+                                    for (int h = 0; h < 2; ++h) {
+                                        const float4 pk = ld_volatile16(slot + ((u0 + u) * 2 + h) * NC + threadIdx.x);
+                                        v[j][u][h] = pk;
+                                        ready = ready && __float_as_uint(pk.z) == epoch && __float_as_uint(pk.w) == epoch;
+                                    }
+                            }
+                    }
+                    if (!ready) report(a.status, TF_ESTALL);
 #pragma unroll
                     for (int j = 0; j < SB; ++j)
                         if (j < cnt) {
-                            const float4* slot = reinterpret_cast<const float4*>(a.slots + (size_t)who[j] * (2 * kSlotFloats));
 #pragma unroll
-                            for (int ti = 0; ti < T; ++ti)
-#pragma unroll
-                                for (int rb = 0; rb < MB; ++rb)
-#pragma unroll
-                                    for (int h = 0; h < 2; ++h) {
-                                        const float4 pk = ld_volatile16(slot + ((ti * MB + rb) * 2 + h) * NC + threadIdx.x);
-                                        v[j][ti][rb][h] = pk;
-                                        ready = ready && __float_as_uint(pk.z) == epoch && __float_as_uint(pk.w) == epoch;
-                                    }
+                            for (int u = 0; u < UB; ++u) {
+                                float* ac = acc[(u0 + u) / MB][(u0 + u) % MB];
+                                ac[0] += v[j][u][0].x; ac[1] += v[j][u][0].y;
+                                ac[2] += v[j][u][1].x; ac[3] += v[j][u][1].y;
+                            }
                         }
                 }
-                if (!ready) report(a.status, TF_ESTALL);
-#pragma unroll
-                for (int j = 0; j < SB; ++j)
-                    if (j < cnt) {
-#pragma unroll
-                        for (int ti = 0; ti < T; ++ti)
-#pragma unroll
-                            for (int rb = 0; rb < MB; ++rb) {
-                                acc[ti][rb][0] += v[j][ti][rb][0].x; acc[ti][rb][1] += v[j][ti][rb][0].y;
-                                acc[ti][rb][2] += v[j][ti][rb][1].x; acc[ti][rb][3] += v[j][ti][rb][1].y;
-                            }
-                    }
             }
             if (tr != nullptr && threadIdx.x == 0) stamp(tr, 6);
         }
@@ -432,18 +436,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
     if (threadIdx.x == 0) stamp(tr, 9);
 }
 
-template <class C, bool MULTI, bool FULL>
-int launch_as(const Args& a, cudaStream_t stream);
-
 template <class C, bool MULTI = false>
 int launch(const Args& a, cudaStream_t stream) {
-    return (a.K / 64) % C::KTS == 0 ? launch_as<C, MULTI, true>(a, stream) : launch_as<C, MULTI, false>(a, stream);
-}
-
-template <class C, bool MULTI, bool FULL>
-int launch_as(const Args& a, cudaStream_t stream) {
     static_assert(C::SMEM <= (C::CTAS == 2 ? 113 : 227) * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<C, MULTI, FULL>;
+    auto kern = qmm_kernel<C, MULTI>;
     // the opt-in is per device: keep one flag per device ordinal
     static bool configured[64] = {};
     int dev = 0;
@@ -479,7 +475,7 @@ int dispatch(const Args& a, cudaStream_t stream) {
     // loads; the wider buckets are bound by the tensor pipe and keep one tile a warp (their accumulators
     // take the registers)
     if (a.M <= 8) return launch<Cfg<G, 1, 4, 2, 1>>(a, stream);
-    if (a.M <= 16) return launch<Cfg<G, 2, 4, 2, 1>>(a, stream);
+    if (a.M <= 16) return launch<Cfg<G, 2, 4, 1, 1>>(a, stream);
     if (a.M <= 32) return launch<Cfg<G, 4, 4, 1, 1>>(a, stream);
     if (a.M <= 64) return launch<Cfg<G, 8, 2, 1, 1>>(a, stream);
     return launch<Cfg<G, 16, 2, 1, 1>>(a, stream);
@@ -607,7 +603,7 @@ int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratc
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
     if (!x_packed || !w_tiled || !y) return TF_EINVAL;
-    const long long CB = (N + tf::kCols - 1) / tf::kCols, SPB = (K / 64 + tf::kItemTiles - 1) / tf::kItemTiles;
+    const long long CB = (N + tf::kCols - 1) / tf::kCols, IT = tf::item_tiles_for((int)CB, K / 64), SPB = (K / 64 + IT - 1) / IT;
     if (CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
     if ((uintptr_t)y & 3) return TF_EALIGN;

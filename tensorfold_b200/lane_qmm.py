@@ -23,7 +23,7 @@ from . import _lib
 MAX_ROWS = 128           # rows one kernel launch accepts (reference: lane_qmm.MAX_ROWS)
 WORKERS = 148            # persistent CTAs the K schedule is cut for (a library constant, not the device's SM count)
 COLUMN_BLOCK = 256       # output columns per column block
-ITEM_TILES = 4           # 64-input k tiles per schedule item, the same for every row count
+MAX_CUTS_NARROW = 8      # a weight of fewer than 18 column blocks is cut into at most this many items a block
 
 
 @dataclass
@@ -97,9 +97,9 @@ def segments(n: int, k: int) -> list[list[tuple[int, int]]]:
     formed separately and then added in order. A function of the shape and the worker count only —
     never of the row count."""
 
-    kts = ITEM_TILES
     kt = k // 64
     cb = -(-n // COLUMN_BLOCK)
+    kts = -(-kt // MAX_CUTS_NARROW) if cb * MAX_CUTS_NARROW < WORKERS else 1     # k tiles per schedule item
     spb = -(-kt // kts)
     total = cb * spb
     bounds = [i * total // WORKERS for i in range(WORKERS + 1)]
