@@ -329,11 +329,16 @@ int tf_kv_commit(const void* k_new, const void* v_new, long long rec_stride, voi
  *   as local slot experts / world with its problems dealt round-robin. tf_moe_group then also writes
  *   prob_sel (this rank's problems, ascending) and sel_count, and prob_expert holds local slots: pass
  *   prob_sel / sel_count to tf_qmm_grouped. tf_moe_push stores the rank's results as 16-byte packets
- *   {value, n, value, n} into EVERY rank's buffer (peer_bufs as for tf_peer_exchange; a slot is
- *   max_probs * 8 * D * 8 bytes, zero before first use) at the problem's own index; tf_moe_combine_peer
- *   polls the packets its pairs need (bounded, TF_ESTALL) and combines as tf_moe_combine does - the
- *   result has the bits of the one-GPU block. seq and tickets as for tf_peer_exchange; consecutive
- *   exchanges alternate between two slots. */
+ *   {value, n, value, n} into EVERY rank's buffer (peer_bufs as for tf_peer_exchange) at the problem's
+ *   own index, and - also when the rank owns no problem - one presence cell {n, n, n, n} for `rank` at the
+ *   head of every rank's slot. A buffer is two slots of slot_bytes >= tf_moe_slot_bytes(max_probs, D)
+ *   (1024 bytes of presence cells, then max_probs * 8 * D * 8 bytes of packets), zero before first use;
+ *   the slot of exchange n is n & 1, chosen on the device. tf_moe_combine_peer polls the packets its
+ *   pairs need in this rank's own buffer (bounded, TF_ESTALL) and combines as tf_moe_combine does - the
+ *   result has the bits of the one-GPU block - and advances the exchange number only after all `world`
+ *   presence cells carry n, so a slot is never overwritten while a slower rank still reads it. seq and
+ *   tickets as for tf_peer_exchange; every rank issues one push and one combine per exchange. */
+size_t tf_moe_slot_bytes(int max_probs, int D);
 int tf_moe_max_problems(int rows, int slots, int experts_total);
 int tf_moe_router(const void* x, size_t x_stride, const void* router, float* logits, int rows, int D, int experts_total,
                   void* stream);
@@ -345,9 +350,9 @@ int tf_moe_pack(const void* x, size_t x_stride, const int* prob_rows, const int*
 int tf_moe_act(const void* gate_up, const int* prob_count, int max_probs, void* act_packed, int I, int group, void* stream);
 int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* stream);
 int tf_moe_push(const float* y, const int* prob_sel, const int* sel_count, int max_probs, int D, void* const* peer_bufs,
-                size_t slot_off, int world, const void* seq, void* stream);
-int tf_moe_combine_peer(const void* packets, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* seq,
-                        void* tickets, int* status, void* stream);
+                size_t slot_bytes, int rank, int world, const void* seq, void* stream);
+int tf_moe_combine_peer(const void* my_buf, size_t slot_bytes, const int* pair_loc, const float* wts, int slots, void* out, int rows,
+                        int D, int world, void* seq, void* tickets, int* status, void* stream);
 
 /* ---- tensor-parallel exchange over peer memory ---------------------------------------------------
  * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (gather_rank_partials over NCCL) and the
@@ -357,13 +362,36 @@ int tf_moe_combine_peer(const void* packets, const int* pair_loc, const float* w
  * and stored into block `rank` of the slot at slot_off of EVERY rank's buffer (peer_bufs: device array
  * of the world's buffer base addresses, the same symmetric allocation on every rank, zero before the
  * first exchange); each rank then polls its own slot until every packet carries n and writes the
- * payload to `gathered` [world, rows, D] fp32 (local memory). A slot is tf_peer_slot_bytes bytes.
+ * payload to `gathered` [world, rows, D] fp32 (local memory). A slot is at least tf_peer_slot_bytes bytes.
  * seq and tickets: one zero-initialised 32-bit word each in local device memory, private to this rank
  * group. Consecutive exchanges must alternate between two slots; all ranks must issue the same
- * exchanges in the same order. The polling is bounded and reports TF_ESTALL through `status`. */
+ * exchanges in the same order; the slot of an exchange is chosen on the device (n & 1), the buffer is
+ * 2 * slot_bytes. The polling is bounded and reports TF_ESTALL through `status`. */
 size_t tf_peer_slot_bytes(int rows, int D, int world);
-int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_off, float* gathered, int rank,
+int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_bytes, float* gathered, int rank,
                      int world, void* seq, void* tickets, int* status, void* stream);
+
+/* The same exchange fused into its neighbours (no kernel of its own, no staging pass): tf_qmm_peer is the
+ * row-parallel matmul whose epilogue stores the rank's fp32 partial as packets {row 2i, n, row 2i+1, n}
+ * straight into block `rank` of slot n & 1 (n = *seq + 1) of EVERY rank's buffer (peer_bufs, plain peer
+ * stores, no multicast); tf_norm_xs_peer is tf_norm_xs whose residual addend is the sum, in rank order with
+ * one rounding, of the `world` partials it finds in this rank's own buffer (my_buf) once their packets
+ * carry n (bounded wait, TF_ESTALL through `status`); its last CTA advances *seq. Every rank must issue the
+ * same sequence of (tf_qmm_peer, tf_norm_xs_peer) pairs; buffers are 2 * slot_bytes, slot_bytes >=
+ * tf_peer_slot_bytes(rows, D, world), zero before first use; seq and tickets: one zeroed 32-bit word each.
+ * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (row_partial + gather_rank_partials +
+ * sum_rank_partials) around the two row-parallel projections of a layer. */
+int tf_qmm_peer(const void* x_packed, const void* w_tiled, void* scratch, size_t scratch_bytes, int M, int N, int K, int group,
+                void* const* peer_bufs, size_t slot_bytes, const void* seq, int rank, int world, const void* next_w_tiled,
+                int next_N, int next_K, int next_group, int* status, void* stream);
+int tf_norm_xs_peer(const void* x, const void* residual, const void* partials, int nparts, size_t part_stride,
+                    const void* weight, void* h_out, void* y_rows, void* y_packed, int M, int D, int group, float eps,
+                    const void* my_buf, size_t slot_bytes, void* seq, void* tickets, int world, int* status, void* stream);
+
+/* Polls of one location another rank writes before a kernel gives up and writes TF_ESTALL (default 2^22,
+ * seconds; 0 restores it). Applies to later launches of this process. The reference has no counterpart:
+ * its collectives time out on the host (families/qwen4_exp/cuda/comm.py:41-85). */
+void tf_set_poll_limit(unsigned polls);
 
 /* ---- exact top-k and keyed sampling --------------------------------------------------------------
  * Each row's k largest bf16 logits (k <= 64), ordered by value descending then id ascending; ties at

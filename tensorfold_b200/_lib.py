@@ -84,15 +84,21 @@ SIGNATURES: dict[str, tuple] = {
     "tf_moe_select": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "tf_moe_group": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_void_p, c_void_p, c_void_p]),
-    "tf_moe_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
-    "tf_moe_combine_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                    c_void_p]),
+    "tf_moe_slot_bytes": (c_size_t, [c_int, c_int]),
+    "tf_moe_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),
+    "tf_moe_combine_peer": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_void_p]),
     "tf_moe_pack": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_act": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tf_peer_slot_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_peer_exchange": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_void_p]),
+    "tf_qmm_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p,
+                            c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "tf_norm_xs_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "tf_set_poll_limit": (None, [ctypes.c_uint]),
     "tf_topk_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_topk_rows": (c_int, [c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tf_sample_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_ulonglong, c_double, c_int, c_double, c_void_p,
@@ -101,8 +107,8 @@ SIGNATURES: dict[str, tuple] = {
 
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
-_NO_LAUNCH = {"tf_version", "tf_qmm_set_trace", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
-              "tf_attention_scratch_bytes", "tf_attention_chunks", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_peer_slot_bytes"}
+_NO_LAUNCH = {"tf_version", "tf_qmm_set_trace", "tf_set_poll_limit", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
+              "tf_attention_scratch_bytes", "tf_attention_chunks", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_moe_slot_bytes", "tf_peer_slot_bytes"}
 
 
 def launch_count() -> int:

@@ -174,6 +174,12 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- bounded polling of memory another rank writes -----------------------------------------------
+// Polls of one location before a kernel gives up and reports TF_ESTALL (each poll is a memory round trip:
+// the default is seconds). tf_set_poll_limit changes it for later launches of this process, so that the
+// run-out path can be exercised in milliseconds.
+inline unsigned& poll_limit_ref() { static unsigned limit = 1u << 22; return limit; }
+
 // ---- launches ------------------------------------------------------------------------------------
 // Kernels can be launched with programmatic stream serialisation: a kernel may then become resident
 // while its predecessor still runs, do its input-independent work (barrier setup, weight prefetch)

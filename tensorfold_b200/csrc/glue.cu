@@ -34,13 +34,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // ---- norm_xs ------------------------------------------------------------------------------------
 // One CTA per row, D/8 threads, 8 elements a thread.
+// Tensor-parallel form: the residual's addend arrives as self-signalling packets in this rank's exchange
+// buffer, written by every rank's row-parallel matmul (tf_qmm_peer): block p of slot n & 1 holds rank p's
+// fp32 partial as {row 2i, n, row 2i+1, n}. The kernel waits (bounded) for the exchange number n = *seq + 1 in
+// every packet it needs, adds the ranks in order and rounds once; the last CTA to finish advances *seq.
+struct PeerIn {
+    const uint8_t* mine;        // this rank's buffer (null: not the peer form)
+    size_t slot_bytes;
+    uint32_t* seq;
+    int* tickets;
+    int* status;
+    int world;
+    unsigned spin_limit;
+};
+
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 template <int G>
 __global__ void norm_xs_kernel(const __nv_bfloat16* x, const __nv_bfloat16* r, const float* parts, int nparts,
                                size_t part_stride, const __nv_bfloat16* w, __nv_bfloat16* h_out,
-                               __nv_bfloat16* y_rows, uint8_t* y_packed, int M, int D, float eps) {
+                               __nv_bfloat16* y_rows, uint8_t* y_packed, int M, int D, float eps, const PeerIn peer) {
     __shared__ float scratch[32];
+    __shared__ int is_last;
     pdl_launch_dependents();
-    pdl_wait();
+    // In the peer form the kernel does NOT wait for its predecessor (the row-parallel matmul) to complete: its
+    // other inputs are older than that, and the matmul's output arrives as packets that announce themselves,
+    // so the wait below is on the data, not on the grid. This hides the completion of the matmul's remote
+    // stores (an NVLink round trip). Whoever runs after this kernel still waits for it, and it ends only
+    // after every rank's packets of this exchange have arrived.
+    if (peer.mine == nullptr) pdl_wait();
     const int row = blockIdx.x, c = threadIdx.x;           // chunk c = elements 8c..8c+7
     if (row >= M) {                                        // padding rows of the packed buffer are zero
         if (y_packed != nullptr) packed_store<G>(y_packed, tf_padded_rows(M), row, c, make_uint4(0, 0, 0, 0), 0.f);
@@ -49,9 +75,37 @@ __global__ void norm_xs_kernel(const __nv_bfloat16* x, const __nv_bfloat16* r, c
     const size_t at = (size_t)row * (D >> 3) + c;
     float h[8];
     unpack8(reinterpret_cast<const uint4*>(x)[at], h);
-    if (r != nullptr || nparts > 0) {
+    if (r != nullptr || nparts > 0 || peer.mine != nullptr) {
         float add[8];
-        if (nparts > 0) {
+        if (peer.mine != nullptr) {
+            const uint32_t want = *reinterpret_cast<volatile uint32_t*>(peer.seq) + 1u;
+            const uint4* slot = reinterpret_cast<const uint4*>(peer.mine + (want & 1u) * peer.slot_bytes);
+            const size_t per_rank = (size_t)((M + 1) / 2) * D;
+            // once a wait has run out anywhere in this process the exchange is lost: do not wait again
+            bool stalled = peer.status != nullptr && *reinterpret_cast<volatile int*>(peer.status) != 0;
+            for (int p = 0; p < peer.world; ++p) {
+                const uint4* src = slot + p * per_rank + (size_t)(row >> 1) * D + 8 * c;
+                uint4 pk[8];
+                bool ready = false;
+                for (unsigned spins = 0; !ready; ++spins) {
+                    ready = true;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        pk[i] = ld_volatile16(src + i);
+                        ready = ready && pk[i].y == want && pk[i].w == want;
+                    }
+                    if (stalled || spins >= peer.spin_limit) { stalled = stalled || !ready; break; }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float v = __uint_as_float((row & 1) ? pk[i].z : pk[i].x);
+                    add[i] = p == 0 ? v : add[i] + v;
+                }
+            }
+            if (stalled) report(peer.status, TF_ESTALL);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) add[i] = round_bf16(add[i]);
+        } else if (nparts > 0) {
             // a row-parallel projection's per-rank fp32 partials: rank order, one rounding
 #pragma unroll
             for (int i = 0; i < 8; ++i) add[i] = 0.f;
@@ -83,6 +137,16 @@ __global__ void norm_xs_kernel(const __nv_bfloat16* x, const __nv_bfloat16* r, c
     if (y_rows != nullptr) reinterpret_cast<uint4*>(y_rows)[at] = yv;
     const float gs = group_sum8<G>(yv);
     if (y_packed != nullptr) packed_store<G>(y_packed, tf_padded_rows(M), row, c, yv, gs);
+    if (peer.mine != nullptr) {
+        // every live row's CTA has read the exchange number by now; the last one to get here advances it
+        __syncthreads();
+        if (threadIdx.x == 0) is_last = atomicAdd(peer.tickets, 1) == M - 1;
+        __syncthreads();
+        if (is_last && threadIdx.x == 0) {
+            *peer.tickets = 0;
+            *reinterpret_cast<volatile uint32_t*>(peer.seq) = *reinterpret_cast<volatile uint32_t*>(peer.seq) + 1u;
+        }
+    }
 }
 
 // ---- swiglu: rows x (I/8) threads -----------------------------------------------------------------
@@ -312,13 +376,25 @@ extern "C" {
 
 int tf_norm_xs(const void* x, const void* residual, const void* partials, int nparts, size_t part_stride, const void* weight,
                void* h_out, void* y_rows, void* y_packed, int M, int D, int group, float eps, void* stream) {
+    return tf_norm_xs_peer(x, residual, partials, nparts, part_stride, weight, h_out, y_rows, y_packed, M, D, group, eps, nullptr, 0,
+                           nullptr, nullptr, 0, nullptr, stream);
+}
+
+int tf_norm_xs_peer(const void* x, const void* residual, const void* partials, int nparts, size_t part_stride, const void* weight,
+                    void* h_out, void* y_rows, void* y_packed, int M, int D, int group, float eps, const void* my_buf,
+                    size_t slot_bytes, void* seq, void* tickets, int world, int* status, void* stream) {
+    if (my_buf && (residual || nparts > 0 || !seq || !tickets || world < 2 || world > 64 || ((uintptr_t)my_buf & 15) || (slot_bytes & 15)))
+        return TF_EINVAL;
+    if (my_buf && slot_bytes < tf_peer_slot_bytes(M, D, world)) return TF_EINVAL;
     if (M < 1 || M > TF_QMM_MAX_ROWS || D < 256 || D % 256 || D > 8192 || (group != 64 && group != 32)) return TF_EINVAL;
     if (!x || !weight || nparts < 0 || (nparts > 0 && !partials) || (residual && nparts > 0)) return TF_EINVAL;
-    if ((residual || nparts > 0) && !h_out) return TF_EINVAL;
+    if ((residual || nparts > 0 || my_buf) && !h_out) return TF_EINVAL;
     if (((uintptr_t)x | (uintptr_t)residual | (uintptr_t)partials | (uintptr_t)weight | (uintptr_t)h_out |
          (uintptr_t)y_rows | (uintptr_t)y_packed) & 15) return TF_EALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    void* args[] = {&x, &residual, &partials, &nparts, &part_stride, &weight, &h_out, &y_rows, &y_packed, &M, &D, &eps};
+    tf::PeerIn peer = {static_cast<const uint8_t*>(my_buf), slot_bytes, static_cast<uint32_t*>(seq), static_cast<int*>(tickets),
+                       status, world, tf::poll_limit_ref()};
+    void* args[] = {&x, &residual, &partials, &nparts, &part_stride, &weight, &h_out, &y_rows, &y_packed, &M, &D, &eps, &peer};
     const void* fn = group == 64 ? (const void*)tf::norm_xs_kernel<64> : (const void*)tf::norm_xs_kernel<32>;
     return tf::finish(tf::launch_pdl(fn, dim3(y_packed ? tf::tf_padded_rows(M) : M), dim3(D / 8), 0, st, args, 2));
 }

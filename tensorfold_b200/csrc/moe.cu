@@ -284,9 +284,18 @@ __global__ void moe_combine_kernel(const float* y, const int* pair_loc, const fl
 
 // ---- expert parallelism: results of a rank's own problems to every rank, then the combine --------------
 // Packets as in the tensor-parallel exchange: 16 bytes {value, n, value, n}, n = the exchange number. A
-// problem has one owner, so every rank's buffer is one array indexed like the compact results
+// problem has one owner, so the data part of every rank's slot is one array indexed like the compact results
 // ([problem * 8 + place][D / 2] packets) and nobody writes another's entries. The combine polls exactly
 // the packets its pairs need (bounded) and adds a row's slots in slot order, as on one GPU.
+//
+// A slot starts with kPresenceBytes of presence cells, one 16-byte cell {n, n, n, n} per source rank. Every
+// rank writes its cell into every rank's slot in EVERY exchange, also when it owns no problem, and a combine
+// advances the exchange number only after it has seen all `world` cells carry n. So a rank that has passed
+// combine n+1 knows that every rank has issued push n+1, which each issues only after its combine n completed:
+// nobody still reads the slot of exchange n when exchange n+2 is pushed into it. The slot of an exchange is
+// (n & 1), chosen on the device, so a captured graph with an odd number of exchanges still alternates.
+constexpr size_t kPresenceBytes = 1024;      // 64 ranks x 16 bytes
+
 __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -297,41 +306,47 @@ __device__ __forceinline__ void st_volatile16(uint4* p, uint4 v) {
 }
 
 __global__ void __launch_bounds__(256) moe_push_kernel(const float2* y, const int* prob_sel, const int* sel_count, int D2,
-                                                       uint8_t* const* bufs, size_t slot_off, int world, const uint32_t* seq) {
+                                                       uint8_t* const* bufs, size_t slot_bytes, int rank, int world,
+                                                       const uint32_t* seq) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(seq) + 1u;
+    const size_t slot_off = (want & 1u) * slot_bytes;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (int)threadIdx.x < world)
+        st_volatile16(reinterpret_cast<uint4*>(bufs[threadIdx.x] + slot_off) + rank, make_uint4(want, want, want, want));
     const int n = sel_count[0];
     for (int q = blockIdx.y; q < n; q += gridDim.y) {
         const size_t base = (size_t)prob_sel[q] * 8 * D2;
         for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 8 * D2; i += gridDim.x * blockDim.x) {
             const float2 v = y[base + i];
             const uint4 pkt = make_uint4(__float_as_uint(v.x), want, __float_as_uint(v.y), want);
-            for (int peer = 0; peer < world; ++peer) st_volatile16(reinterpret_cast<uint4*>(bufs[peer] + slot_off) + base + i, pkt);
+            for (int peer = 0; peer < world; ++peer)
+                st_volatile16(reinterpret_cast<uint4*>(bufs[peer] + slot_off + kPresenceBytes) + base + i, pkt);
         }
     }
 }
 
-constexpr unsigned kPollLimit = 1u << 22;
-
-__global__ void moe_combine_peer_kernel(const uint4* packets, const int* pair_loc, const float* wts, int slots, __nv_bfloat16* out, int R,
-                                        int D, uint32_t* seq, int* tickets, int* status) {
+__global__ void moe_combine_peer_kernel(const uint8_t* my_buf, size_t slot_bytes, const int* pair_loc, const float* wts, int slots,
+                                        __nv_bfloat16* out, int R, int D, int world, uint32_t* seq, int* tickets, int* status,
+                                        unsigned spin_limit) {
     __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t want = *reinterpret_cast<volatile uint32_t*>(seq) + 1u;
+    const uint4* cells = reinterpret_cast<const uint4*>(my_buf + (want & 1u) * slot_bytes);
+    const uint4* packets = reinterpret_cast<const uint4*>(my_buf + (want & 1u) * slot_bytes + kPresenceBytes);
     const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;       // c: a pair of packets = 4 values
+    // once a wait has run out anywhere in this process the exchange is lost: do not wait again
+    bool stalled = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
     if (c < (D >> 2) && r < R) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        // once a wait has run out anywhere in this process the exchange is lost: do not wait again
-        bool stalled = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
         for (int k = 0; k < slots; ++k) {
             const float w = wts[(size_t)r * slots + k];
             const uint4* src = packets + (size_t)pair_loc[r * slots + k] * (D >> 1) + 2 * c;
             uint4 a = ld_volatile16(src), b = ld_volatile16(src + 1);
             unsigned spins = 0;
             while ((a.y != want || a.w != want || b.y != want || b.w != want) && !stalled) {
-                if (++spins > kPollLimit) { stalled = true; break; }
+                if (++spins > spin_limit) { stalled = true; break; }
                 a = ld_volatile16(src);
                 b = ld_volatile16(src + 1);
             }
@@ -340,17 +355,30 @@ __global__ void moe_combine_peer_kernel(const uint4* packets, const int* pair_lo
             acc.z = __fmaf_rn(w, __uint_as_float(b.x), acc.z);
             acc.w = __fmaf_rn(w, __uint_as_float(b.z), acc.w);
         }
-        if (stalled) report(status, TF_ESTALL);
         __nv_bfloat16* o = out + (size_t)r * D + 4 * c;
         *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc.x, acc.y);
         *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
     }
+    if (stalled) report(status, TF_ESTALL);
     __syncthreads();
     if (threadIdx.x == 0) is_last = atomicAdd(tickets, 1) == (int)(gridDim.x * gridDim.y) - 1;
     __syncthreads();
-    if (is_last && threadIdx.x == 0) {
-        *tickets = 0;
-        *reinterpret_cast<volatile uint32_t*>(seq) = want;
+    if (is_last) {
+        // every rank's presence cell, also of ranks that sent this rank no data
+        if ((int)threadIdx.x < world) {
+            uint4 cell = ld_volatile16(cells + threadIdx.x);
+            unsigned spins = 0;
+            while ((cell.x != want || cell.y != want || cell.z != want || cell.w != want) && !stalled) {
+                if (++spins > spin_limit) { stalled = true; break; }
+                cell = ld_volatile16(cells + threadIdx.x);
+            }
+            if (stalled) report(status, TF_ESTALL);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            *tickets = 0;
+            *reinterpret_cast<volatile uint32_t*>(seq) = want;
+        }
     }
 }
 
@@ -425,28 +453,36 @@ int tf_moe_combine(const float* y, const int* pair_loc, const float* wts, int sl
                           static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }
 
+size_t tf_moe_slot_bytes(int max_probs, int D) {
+    if (max_probs < 1 || D < 4) return 0;
+    return tf::kPresenceBytes + (size_t)max_probs * 8 * D * 8;      // presence cells, then a packet per two fp32 values
+}
+
 int tf_moe_push(const float* y, const int* prob_sel, const int* sel_count, int max_probs, int D, void* const* peer_bufs,
-                size_t slot_off, int world, const void* seq, void* stream) {
-    if (max_probs < 1 || D < 4 || D % 4 || world < 2 || world > 64 || !y || !prob_sel || !sel_count || !peer_bufs || !seq) return TF_EINVAL;
-    if (((uintptr_t)y | slot_off) & 15) return TF_EALIGN;
+                size_t slot_bytes, int rank, int world, const void* seq, void* stream) {
+    if (max_probs < 1 || D < 4 || D % 4 || world < 2 || world > 64 || rank < 0 || rank >= world) return TF_EINVAL;
+    if (!y || !prob_sel || !sel_count || !peer_bufs || !seq || slot_bytes < tf_moe_slot_bytes(max_probs, D)) return TF_EINVAL;
+    if (((uintptr_t)y | slot_bytes) & 15) return TF_EALIGN;
     const float2* src = reinterpret_cast<const float2*>(y);
     int d2 = D / 2;
     uint8_t* const* bufs = reinterpret_cast<uint8_t* const*>(peer_bufs);
     const uint32_t* seq_p = static_cast<const uint32_t*>(seq);
     int by = max_probs < 64 ? max_probs : 64;
-    void* args[] = {&src, &prob_sel, &sel_count, &d2, &bufs, &slot_off, &world, &seq_p};
+    void* args[] = {&src, &prob_sel, &sel_count, &d2, &bufs, &slot_bytes, &rank, &world, &seq_p};
     return tf::launch_pdl((const void*)tf::moe_push_kernel, dim3(2, by), dim3(256), 0, static_cast<cudaStream_t>(stream), args) ==
                    cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }
 
-int tf_moe_combine_peer(const void* packets, const int* pair_loc, const float* wts, int slots, void* out, int rows, int D, void* seq,
-                        void* tickets, int* status, void* stream) {
-    if (rows < 1 || rows > 65535 || slots < 1 || D < 8 || D % 8 || !packets || !pair_loc || !wts || !out || !seq || !tickets) return TF_EINVAL;
-    if (((uintptr_t)packets | (uintptr_t)out) & 15) return TF_EALIGN;
-    const uint4* pk = static_cast<const uint4*>(packets);
+int tf_moe_combine_peer(const void* my_buf, size_t slot_bytes, const int* pair_loc, const float* wts, int slots, void* out, int rows,
+                        int D, int world, void* seq, void* tickets, int* status, void* stream) {
+    if (rows < 1 || rows > 65535 || slots < 1 || D < 8 || D % 8 || world < 2 || world > 64) return TF_EINVAL;
+    if (!my_buf || !pair_loc || !wts || !out || !seq || !tickets || slot_bytes <= tf::kPresenceBytes) return TF_EINVAL;
+    if (((uintptr_t)my_buf | (uintptr_t)out | slot_bytes) & 15) return TF_EALIGN;
+    const uint8_t* buf = static_cast<const uint8_t*>(my_buf);
     uint32_t* seq_p = static_cast<uint32_t*>(seq);
     int* tick_p = static_cast<int*>(tickets);
-    void* args[] = {&pk, &pair_loc, &wts, &slots, &out, &rows, &D, &seq_p, &tick_p, &status};
+    unsigned limit = tf::poll_limit_ref();
+    void* args[] = {&buf, &slot_bytes, &pair_loc, &wts, &slots, &out, &rows, &D, &world, &seq_p, &tick_p, &status, &limit};
     return tf::launch_pdl((const void*)tf::moe_combine_peer_kernel, dim3((D / 4 + 255) / 256, rows), dim3(256), 0,
                           static_cast<cudaStream_t>(stream), args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }

@@ -13,7 +13,8 @@
 //           plain [world, rows, D] fp32 array the next kernel reads.
 // The exchange number is a device counter every rank advances identically; 8-byte halves of a packet
 // are written atomically, and a stale packet carries an older number, so a reader never mixes
-// exchanges. Slots alternate (chosen by the host, fixed per launch): a rank can only push exchange
+// exchanges. Slots alternate (chosen on the device from the exchange number, so a captured graph with an odd
+// number of exchanges still alternates across replays): a rank can only push exchange
 // n+2 into the slot of n after passing the gather of n+1, which needs every rank's push of n+1, which
 // each rank issues only after it has consumed n.
 // The sum itself (rank order, one rounding) is fused into the kernel that consumes the partials.
@@ -25,8 +26,6 @@
 namespace tf {
 namespace {
 
-constexpr unsigned kSpinLimit = 1u << 22;     // polls of one packet (each a memory round trip): seconds, then TF_ESTALL
-
 __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -37,13 +36,14 @@ __device__ __forceinline__ void st_volatile16(uint4* p, uint4 v) {
 }
 
 // n2 = rows * D / 2 packets per rank block
-__global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local, int n2, uint8_t* const* bufs, size_t slot_off,
+__global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local, int n2, uint8_t* const* bufs, size_t slot_bytes,
                                                             float2* gathered, int rank, int world, uint32_t* seq, int* tickets,
-                                                            int* status) {
+                                                            int* status, unsigned spin_limit) {
     __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t want = *reinterpret_cast<volatile uint32_t*>(seq) + 1u;
+    const size_t slot_off = (want & 1u) * slot_bytes;      // consecutive exchanges alternate, whatever the host captured
     const int stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
     for (int i = first; i < n2; i += stride) {
         const float2 v = local[i];
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local,
             uint4 pkt = ld_volatile16(mine + (size_t)r * n2 + i);
             unsigned spins = 0;
             while ((pkt.y != want || pkt.w != want) && !stalled) {
-                if (++spins > kSpinLimit) { stalled = true; break; }
+                if (++spins > spin_limit) { stalled = true; break; }
                 pkt = ld_volatile16(mine + (size_t)r * n2 + i);
             }
             gathered[(size_t)r * n2 + i] = make_float2(__uint_as_float(pkt.x), __uint_as_float(pkt.z));
@@ -80,16 +80,19 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const float2* local,
 
 extern "C" {
 
+void tf_set_poll_limit(unsigned polls) { tf::poll_limit_ref() = polls ? polls : (1u << 22); }
+
 size_t tf_peer_slot_bytes(int rows, int D, int world) {
     if (rows < 1 || D < 2 || world < 1) return 0;
-    return (size_t)world * rows * D * 8;            // a 16-byte packet per two fp32 values
+    return (size_t)world * ((rows + 1) / 2) * D * 16;   // a 16-byte packet per two fp32 values (rows in pairs, rounded up)
 }
 
-int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_off, float* gathered, int rank,
+int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs, size_t slot_bytes, float* gathered, int rank,
                      int world, void* seq, void* tickets, int* status, void* stream) {
     if (rows < 1 || D < 4 || D % 4 || world < 2 || world > 64 || rank < 0 || rank >= world) return TF_EINVAL;
     if (!local || !peer_bufs || !gathered || !seq || !tickets) return TF_EINVAL;
-    if (((uintptr_t)local | (uintptr_t)gathered | slot_off) & 15) return TF_EALIGN;
+    if (((uintptr_t)local | (uintptr_t)gathered | slot_bytes) & 15) return TF_EALIGN;
+    if (slot_bytes < (size_t)world * rows * D * 8) return TF_EINVAL;
     const float2* src = reinterpret_cast<const float2*>(local);
     float2* dst = reinterpret_cast<float2*>(gathered);
     int n2 = rows * (D / 2);
@@ -98,7 +101,8 @@ int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs
     uint8_t* const* bufs = reinterpret_cast<uint8_t* const*>(peer_bufs);
     int blocks = (n2 + 255) / 256;
     if (blocks > 64) blocks = 64;      // few enough to be resident together beside the neighbouring kernels
-    void* args[] = {&src, &n2, &bufs, &slot_off, &dst, &rank, &world, &seq_p, &tick_p, &status};
+    unsigned limit = tf::poll_limit_ref();
+    void* args[] = {&src, &n2, &bufs, &slot_bytes, &dst, &rank, &world, &seq_p, &tick_p, &status, &limit};
     return tf::launch_pdl((const void*)tf::peer_exchange_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
                           args) == cudaSuccess ? TF_OK : (cudaGetLastError(), TF_ECUDA);
 }

@@ -113,6 +113,13 @@ struct Args {
     // issued, each worker asks L2 for the first bytes the SAME worker of that launch will stream
     const uint8_t* next_w;
     int next_N, next_K, next_group, prefetch_bytes;
+    // tensor-parallel partial (may be null): instead of y, the fp32 sums go as 16-byte packets
+    // {row 2i, n, row 2i+1, n} (n = exchange number = *peer_seq + 1) into block peer_rank of slot n & 1 of
+    // EVERY rank's exchange buffer (plain peer stores); the consuming norm kernel waits for the number
+    uint8_t* const* peer_bufs;
+    const uint32_t* peer_seq;
+    size_t peer_slot_bytes;
+    int peer_rank, peer_world;
     const int* prob_expert;
     const int* prob_count;
     const int* prob_sel;
@@ -417,6 +424,30 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             if (tr != nullptr && threadIdx.x == 0) stamp(tr, 6);
         }
         // a whole block, or a finished one: write the output
+        if (!MULTI && a.peer_bufs != nullptr) {
+            // a tensor-parallel rank's partial: straight into every rank's exchange buffer, self-signalling
+            const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(a.peer_seq) + 1u;
+            const size_t base = (want & 1u) * a.peer_slot_bytes + (size_t)a.peer_rank * ((a.M + 1) / 2) * a.N * 16;
+#pragma unroll
+            for (int ti = 0; ti < T; ++ti) {
+                const int col0 = cb * kCols + (warp * T + ti) * 16 + g;
+#pragma unroll
+                for (int rb = 0; rb < MB; ++rb)
+#pragma unroll
+                    for (int hsel = 0; hsel < 2; ++hsel) {
+                        const int row = rb * 8 + 2 * t, col = col0 + hsel * 8;
+                        if (row < a.M && col < a.N) {
+                            const uint4 pkt = make_uint4(__float_as_uint(acc[ti][rb][2 * hsel]), want,
+                                                         __float_as_uint(acc[ti][rb][2 * hsel + 1]), want);
+                            const size_t at = base + ((size_t)(row >> 1) * a.N + col) * 16;
+                            for (int peer = 0; peer < a.peer_world; ++peer)
+                                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(a.peer_bufs[peer] + at), "r"(pkt.x),
+                                             "r"(pkt.y), "r"(pkt.z), "r"(pkt.w) : "memory");
+                        }
+                    }
+            }
+            continue;
+        }
 #pragma unroll
         for (int ti = 0; ti < T; ++ti) {
             const int col0 = cb * kCols + (warp * T + ti) * 16 + g;
@@ -464,6 +495,15 @@ int launch(const Args& a, cudaStream_t stream) {
 }
 
 // bytes of the next matmul's weight each worker asks L2 for (TF_QMM_PREFETCH_KB, default the ring's size)
+// the peer destination of the launch being set up (tf_qmm_peer hands it to tf_qmm_next on the same thread)
+struct PeerOut {
+    uint8_t* const* bufs = nullptr;
+    const uint32_t* seq = nullptr;
+    size_t slot_bytes = 0;
+    int rank = 0, world = 0;
+};
+thread_local PeerOut g_peer;
+
 inline int prefetch_bytes() {
     static const int v = [] { const char* e = std::getenv("TF_QMM_PREFETCH_KB"); return (e ? atoi(e) : 224) * 1024; }();
     return v;
@@ -602,7 +642,7 @@ int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratc
     if (M < 1 || M > TF_QMM_MAX_ROWS || N < 1 || K < 64 || K % 64) return TF_EINVAL;
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
-    if (!x_packed || !w_tiled || !y) return TF_EINVAL;
+    if (!x_packed || !w_tiled || (!y && tf::g_peer.bufs == nullptr)) return TF_EINVAL;
     const long long CB = (N + tf::kCols - 1) / tf::kCols, IT = tf::item_tiles_for((int)CB, K / 64), SPB = (K / 64 + IT - 1) / IT;
     if (CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
@@ -622,8 +662,26 @@ int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratc
     a.w_stride = a.xp_stride = a.y_stride = 0;
     a.next_w = static_cast<const uint8_t*>(next_w_tiled); a.next_N = next_N; a.next_K = next_K; a.next_group = next_group;
     a.prefetch_bytes = tf::prefetch_bytes();
+    a.peer_bufs = tf::g_peer.bufs; a.peer_seq = tf::g_peer.seq; a.peer_slot_bytes = tf::g_peer.slot_bytes;
+    a.peer_rank = tf::g_peer.rank; a.peer_world = tf::g_peer.world;
+    tf::g_peer = tf::PeerOut();
+    if (a.peer_bufs != nullptr) a.y = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return group == 64 ? tf::dispatch<64>(a, st) : tf::dispatch<32>(a, st);
+}
+
+int tf_qmm_peer(const void* x_packed, const void* w_tiled, void* scratch, size_t scratch_bytes, int M, int N, int K, int group,
+                void* const* peer_bufs, size_t slot_bytes, const void* seq, int rank, int world, const void* next_w_tiled,
+                int next_N, int next_K, int next_group, int* status, void* stream) {
+    if (!peer_bufs || !seq || world < 2 || world > 64 || rank < 0 || rank >= world) return TF_EINVAL;
+    if (slot_bytes < tf_peer_slot_bytes(M, N, world) || (slot_bytes & 15)) return TF_EINVAL;
+    tf::g_peer.bufs = reinterpret_cast<uint8_t* const*>(peer_bufs);
+    tf::g_peer.seq = static_cast<const uint32_t*>(seq);
+    tf::g_peer.slot_bytes = slot_bytes; tf::g_peer.rank = rank; tf::g_peer.world = world;
+    const int rc = tf_qmm_next(x_packed, w_tiled, nullptr, scratch, scratch_bytes, M, N, K, group, TF_QMM_F32_OUT, next_w_tiled, next_N,
+                               next_K, next_group, status, stream);
+    tf::g_peer = tf::PeerOut();
+    return rc;
 }
 
 int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_expert, const int* prob_count,
@@ -650,6 +708,7 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.f32_out = (flags & TF_QMM_F32_OUT) ? 1 : 0;
     a.prob_expert = prob_expert; a.prob_count = prob_count; a.prob_sel = prob_sel; a.max_probs = max_probs;
     a.next_w = nullptr; a.next_N = a.next_K = a.next_group = a.prefetch_bytes = 0;
+    a.peer_bufs = nullptr; a.peer_seq = nullptr; a.peer_slot_bytes = 0; a.peer_rank = a.peer_world = 0;
     a.w_stride = (long long)tf_qmm_tiled_bytes(N, K, group);
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;

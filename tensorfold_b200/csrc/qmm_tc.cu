@@ -601,11 +601,14 @@ int launch(const Args& a, cudaStream_t stream) {
     using C = Cfg<G, NB, KTS, STAGES, UPS>;
     static_assert(C::SMEM <= 227 * 1024, "stage ring does not fit shared memory");
     auto kern = qmm_kernel<G, NB, KTS, STAGES, UPS>;
-    static bool configured = false;   // per instantiation; the attribute is per function and idempotent
-    if (!configured) {
+    // the opt-in is per device: keep one flag per device ordinal
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return TF_ECUDA; }
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
             return TF_ECUDA;
-        configured = true;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kWorkers);

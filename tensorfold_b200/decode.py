@@ -183,4 +183,72 @@ def draft_decode(w: Weights, st: State, prompts: Sequence[Sequence[int]], pendin
     return DecodeResult([o[:count] for o in out], time.perf_counter() - start, rounds, drafted, accepted, widths_log)
 
 
-__all__ = ["CopyIndex", "DecodeResult", "draft_decode", "prefill", "serial_decode"]
+class Engine:
+    """The engine contract the reference's server drives (``cuda/server.py:9-15``): ``eos`` and
+    ``generate(prompt, max_tokens, sampling, on_tokens) -> dict`` for one request at a time, decoded as one
+    exact stream: prefill through the lane forward, then drafted rounds (n-gram copy drafter) whose output is
+    token for token what serial decoding gives. A prompt that extends the previous request's reuses its
+    committed state (``State.snapshot`` / ``restore`` at the end of the shared prefix is the caller's tool for
+    anything finer)."""
+
+    def __init__(self, w: Weights, *, max_context: int = 8192, eos: Sequence[int] = (), max_rows: int = 8):
+        self.w, self.eos, self.max_rows, self.max_context = w, tuple(int(t) for t in eos), max_rows, max_context
+        self.state = State(w, 1, max_context)
+        self.committed: list = []              # tokens whose state is committed
+
+    def _reset(self) -> None:
+        self.state.kv.release(0)
+        self.state = State(self.w, 1, self.max_context)
+        self.committed = []
+
+    def generate(self, prompt: Sequence[int], max_tokens: int, sampling: Sampling | None = None,
+                 on_tokens: Callable[[list], bool] | None = None) -> dict:
+        prompt = [int(t) for t in prompt]
+        if not prompt or max_tokens < 1 or len(prompt) + max_tokens > self.max_context:
+            raise ValueError("generate: needs a non-empty prompt that fits the context with max_tokens")
+        keep = len(self.committed)
+        if keep == 0 or keep >= len(prompt) or prompt[:keep] != self.committed:
+            self._reset()
+            keep = 0
+        start = time.perf_counter()
+        pending = prefill(self.w, self.state, [prompt[keep:]], sampling)[0] if keep == 0 else None
+        if pending is None:
+            # the shared prefix is committed already: only the new tail runs; positions continue from it
+            pending = _prefill_tail(self.w, self.state, prompt[keep:], sampling)
+        self.committed = list(prompt)
+        out = [int(pending)]
+        stopped = bool(on_tokens(list(out))) if on_tokens else False
+        rounds = 0
+        while not stopped and len(out) < max_tokens and out[-1] not in self.eos:
+            want = min(max_tokens - len(out) + 1, 4 * self.max_rows)
+            res = draft_decode(self.w, self.state, [self.committed], [out[-1]], want, sampling, max_rows=self.max_rows)
+            new = res.tokens[0][1:]
+            for i, t in enumerate(new):                # stop at the first end token
+                if t in self.eos:
+                    new = new[:i + 1]
+                    break
+            # draft_decode committed every token it emitted but the last: mirror that in the bookkeeping
+            self.committed.extend([out[-1]] + res.tokens[0][1:-1])
+            if len(new) < len(res.tokens[0]) - 1:
+                self._reset()                          # tokens past the end token were committed: start clean next time
+            out.extend(new)
+            rounds += res.rounds
+            if on_tokens and new:
+                stopped = bool(on_tokens(list(new)))
+        return {"tokens": out[:max_tokens], "seconds": time.perf_counter() - start, "rounds": rounds, "prompt_tokens": len(prompt)}
+
+
+def _prefill_tail(w: Weights, st: State, tail: Sequence[int], sampling: Sampling | None, chunk: int = 8) -> int:
+    dev = w.norm.device
+    done, pending = 0, 0
+    while done < len(tail):
+        n = min(chunk, len(tail) - done)
+        logits, rec = tree_forward(w, _tokens(tail[done:done + n], dev), [n], st)
+        if done + n == len(tail):
+            pending = int(sample_rows(logits[n - 1:n].contiguous(), [st.lens[0] + n], sampling).tolist()[0])
+        commit(st, rec, [n])
+        done += n
+    return pending
+
+
+__all__ = ["CopyIndex", "DecodeResult", "Engine", "draft_decode", "prefill", "serial_decode"]

@@ -78,7 +78,7 @@ class RankGroup:
                 raise ValueError("peer exchange needs the hidden size and the device")
             from . import _lib
 
-            self.slot_bytes = _lib.load().tf_peer_slot_bytes(max_rows, hidden, self.world)
+            self.slot_bytes = (_lib.load().tf_peer_slot_bytes(max_rows, hidden, self.world) + 255) // 256 * 256
             self.buf = symm_mem.empty(2 * self.slot_bytes, dtype=torch.uint8, device=device)
             self.buf.zero_()
             self.handle = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
@@ -87,6 +87,41 @@ class RankGroup:
             dist.barrier(group)
         elif exchange != "nccl":
             raise ValueError("exchange must be 'peer' or 'nccl'")
+
+    def check_settings(self, settings: dict) -> None:
+        """Refuse to start when the ranks were given different settings: every rank must issue the same
+        kernels and exchanges in the same order (reference: ``families/qwen3_5/cuda/engine.py:54-62``). The
+        settings travel as one int64 digest per key, gathered by the group's collective."""
+
+        import hashlib
+
+        keys = sorted(settings)
+        mine = torch.tensor([int.from_bytes(hashlib.sha256(f"{k}={settings[k]!r}".encode()).digest()[:7], "big") for k in keys] +
+                            [int.from_bytes(hashlib.sha256(",".join(keys).encode()).digest()[:7], "big")], dtype=torch.int64)
+        dev = self.state.device if self.exchange == "peer" else (torch.device("cuda", torch.cuda.current_device())
+                                                                 if self.dist.get_backend(self.group) == "nccl" else torch.device("cpu"))
+        mine = mine.to(dev)
+        everyone = torch.empty(self.world * mine.numel(), dtype=torch.int64, device=dev)
+        self.dist.all_gather_into_tensor(everyone, mine, group=self.group)
+        everyone = everyone.cpu().reshape(self.world, -1)
+        for r in range(self.world):
+            if not torch.equal(everyone[r], everyone[0]):
+                diff = [k for i, k in enumerate(keys) if everyone[r, i] != everyone[0, i]] or ["the set of settings"]
+                raise RuntimeError(f"ranks were started with different settings: rank {r} differs from rank 0 in {diff}; "
+                                   "every rank must run the same calls in the same order")
+
+    @property
+    def fused(self) -> bool:
+        """Whether the exchange rides inside the row-parallel matmul's epilogue and the next norm kernel
+        (``tf_qmm_peer`` / ``tf_norm_xs_peer``) instead of being a step of its own."""
+
+        return self.exchange == "peer"
+
+    def peer_args(self):
+        """(buffer pointer table, slot bytes, exchange-number word, ticket word, this rank's buffer) for the fused form."""
+
+        return (self.handle.buffer_ptrs_dev, self.slot_bytes, self.state[0:1].data_ptr(), self.state[1:2].data_ptr(),
+                self.buf.data_ptr())
 
     def gather_partials(self, local: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """(M, D) fp32 -> (world, M, D) fp32, rank order."""
@@ -100,13 +135,12 @@ class RankGroup:
             lib = _lib.load()
             if lib.tf_peer_slot_bytes(m, d, self.world) > self.slot_bytes:
                 raise ValueError("partial larger than the exchange buffer")
-            slot_off = (self.count & 1) * self.slot_bytes
             self.count += 1
             local = local.contiguous()
             if out is None:
                 out = torch.empty((self.world, m, d), dtype=torch.float32, device=local.device)
             with torch.cuda.device(local.device):
-                _lib.check(lib.tf_peer_exchange(local.data_ptr(), m, d, self.handle.buffer_ptrs_dev, slot_off, out.data_ptr(), self.rank,
+                _lib.check(lib.tf_peer_exchange(local.data_ptr(), m, d, self.handle.buffer_ptrs_dev, self.slot_bytes, out.data_ptr(), self.rank,
                                                 self.world, self.state[0:1].data_ptr(), self.state[1:2].data_ptr(),
                                                 _lib.status(local.device).word.data_ptr(), _lib.stream()), "peer exchange")
             return out

@@ -5,8 +5,8 @@ Mirror of the reference's ``engine/exact_sampling.py`` (``Sampling``, ``uniform_
 The token at absolute position p is the argmax over the kept candidates of ``logit/T + Gumbel(hash(seed,
 p, id))``: it depends only on the row's own logits and position, so a window row draws the token the
 serial step at that position draws. Candidates come from the GPU radix top-k; the draw runs on the
-GPU too (``tf_sample_rows``). ``choose_rows`` is the same rule on the host in numpy, used where
-candidates from several vocabulary shards are merged (tensor-parallel head).
+GPU too (``tf_sample_rows``); ``choose_rows`` takes candidates in any order (merged vocabulary shards of a
+tensor-parallel head) and draws with the same kernel; there is no host-side draw in this package.
 """
 
 from __future__ import annotations
@@ -31,39 +31,27 @@ class Sampling:
     top_p: float = 0.95
 
 
-def _mix(x: np.ndarray) -> np.ndarray:
-    x = x ^ (x >> np.uint64(30))
-    x = x * np.uint64(0xBF58476D1CE4E5B9)
-    x = x ^ (x >> np.uint64(27))
-    x = x * np.uint64(0x94D049BB133111EB)
-    return x ^ (x >> np.uint64(31))
+def choose_rows(values, ids, positions: Sequence[int], s: Sampling) -> list[int]:
+    """The draw for rows of candidate (value, id) pairs in any order (reference:
+    ``exact_sampling.choose_rows``), run on the GPU: the candidates are put in the order the radix top-k
+    writes them, (value descending, id ascending), and handed to the keyed draw kernel."""
 
-
-def uniform_rows(seed: int, positions: np.ndarray, ids: np.ndarray) -> np.ndarray:
-    """Uniform (0, 1) doubles from a splitmix64 hash of (seed, position, token id), one row per position."""
-
-    with np.errstate(over="ignore"):
-        x = _mix(np.uint64(seed & 0xFFFFFFFFFFFFFFFF) + np.uint64(0x9E3779B97F4A7C15))
-        x = _mix(x ^ (np.asarray(positions).astype(np.uint64)[:, None] * np.uint64(0xD1B54A32D192ED03)))
-        x = _mix(x ^ ids.astype(np.uint64))
-    return (x >> np.uint64(11)).astype(np.float64) * 2.0 ** -53 + 2.0 ** -54
-
-
-def choose_rows(values: np.ndarray, ids: np.ndarray, positions: Sequence[int], s: Sampling) -> list[int]:
-    """Host form of the draw for rows of candidate (value, id) pairs in any order."""
-
-    rows, width = ids.shape
-    order = np.lexsort((ids, -values), axis=-1)
+    dev = torch.device("cuda")
+    val = torch.as_tensor(np.asarray(values), dtype=torch.float32).to(dev)
+    idx = torch.as_tensor(np.asarray(ids).astype(np.int32)).to(dev)
+    rows, width = idx.shape
+    by_id = torch.argsort(idx, dim=-1, stable=True)
+    by_val = torch.argsort(torch.gather(val, 1, by_id), dim=-1, descending=True, stable=True)
+    order = torch.gather(by_id, 1, by_val)
+    idx, val = torch.gather(idx, 1, order).contiguous(), torch.gather(val, 1, order).contiguous()
+    pos = torch.as_tensor(list(positions), dtype=torch.int64).to(dev)
+    tokens = torch.empty(rows, dtype=torch.int32, device=dev)
     k = max(1, min(int(s.top_k) if s.top_k else width, width))
-    ids = np.take_along_axis(ids, order, axis=-1)[:, :k]
-    scaled = np.take_along_axis(values, order, axis=-1)[:, :k].astype(np.float64) / max(float(s.temperature), 1e-6)
-    score = scaled - np.log(-np.log(uniform_rows(s.seed, np.asarray(positions), ids)))
-    if 0.0 < s.top_p < 1.0:
-        probs = np.exp(scaled - scaled.max(axis=-1, keepdims=True))
-        probs /= probs.sum(axis=-1, keepdims=True)
-        keep = (np.cumsum(probs, axis=-1) < s.top_p).sum(axis=-1) + 1
-        score[np.arange(k)[None, :] >= keep[:, None]] = -np.inf
-    return [int(t) for t in ids[np.arange(rows), np.argmax(score, axis=-1)]]
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().tf_sample_rows(idx.data_ptr(), val.data_ptr(), width, pos.data_ptr(), int(s.seed) & 0xFFFFFFFFFFFFFFFF,
+                                              max(float(s.temperature), 1e-6), k, float(s.top_p), tokens.data_ptr(), rows,
+                                              _lib.stream()), "choose_rows")
+    return [int(t) for t in tokens.cpu()]
 
 
 def top_candidates(logits: torch.Tensor, s: Sampling) -> tuple[torch.Tensor, torch.Tensor]:
@@ -100,4 +88,4 @@ def sample_rows(logits: torch.Tensor, positions, s: Sampling | None, *, top: tup
     return tokens
 
 
-__all__ = ["MARGIN", "Sampling", "choose_rows", "sample_rows", "top_candidates", "uniform_rows"]
+__all__ = ["MARGIN", "Sampling", "choose_rows", "sample_rows", "top_candidates"]

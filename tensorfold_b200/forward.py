@@ -173,6 +173,31 @@ class State:
     def sync_lens(self) -> None:
         self.seq_lens.copy_(torch.tensor(self.lens, dtype=torch.int32), non_blocking=True)
 
+    def snapshot(self) -> dict:
+        """What the committed sequences keep outside the K/V pages' rows: the GDN states, the conv tails, the
+        lengths (reference: ``families/qwen4_exp/cuda/forward.py:200-222``). The K/V rows below the lengths stay
+        where they are (later commits only write at or past a sequence's length), so ``restore`` brings the
+        sequences back to this point as long as their pages have not been released. The snapshot carries the
+        kernel library's source hash: state made by other kernels has other bits and is refused."""
+
+        from . import build
+
+        return {"kernels": build.source_hash(), "lens": list(self.lens), "rec": self.rec.clone(), "conv": self.conv.clone()}
+
+    def restore(self, snap: dict) -> None:
+        from . import build
+
+        if snap.get("kernels") != build.source_hash():
+            raise ValueError("State.restore: the snapshot was made by a different build of the kernels")
+        if snap["rec"].shape != self.rec.shape or snap["conv"].shape != self.conv.shape or len(snap["lens"]) != self.n_seqs:
+            raise ValueError("State.restore: the snapshot belongs to a differently shaped state")
+        if any(self.kv.owned[s] * LA.PAGE < n for s, n in enumerate(snap["lens"])):
+            raise ValueError("State.restore: a sequence's pages were released since the snapshot")
+        self.rec.copy_(snap["rec"])
+        self.conv.copy_(snap["conv"])
+        self.lens = list(snap["lens"])
+        self.sync_lens()
+
 
 @dataclass
 class Batch:
@@ -289,11 +314,21 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
     scale = c.head_dim ** -0.5
 
+    fused_tp = tp is not None and getattr(tp, "fused", False)
+
     def row_parallel(act, weight, nxt):
-        """(residual rows, gathered partials): one of the two is None."""
+        """(residual rows, gathered partials): one of the two is None; both are when the exchange is fused
+        into this matmul's epilogue and the next norm kernel."""
         if tp is None:
             return lane_matmul(act, weight, next_weight=nxt), None
+        if fused_tp:
+            lane_matmul(act, weight, next_weight=nxt, peer=tp)
+            return None, None
         return None, tp.gather_partials(lane_matmul(act, weight, f32=True, next_weight=nxt))
+
+    def norm(x_, res, wt, first=False, **kw):
+        # with the fused exchange every norm but the first one (after the embedding) adds a peer sum
+        return lane_glue.norm_xs(x_, res, wt, c.eps, group=g, peer=tp if fused_tp and not first else None, **kw)
 
     # each matmul tells the kernel which weight streams next, so that its first bytes wait in L2
     def after(li):
@@ -303,7 +338,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     pending = parts = None
     gi = ai = 0
     for li, layer in enumerate(w.layers):
-        x, h = lane_glue.norm_xs(x, pending, layer.input_norm, c.eps, group=g, partials=parts)
+        x, h = norm(x, pending, layer.input_norm, first=li == 0, partials=parts)
         if layer.linear:
             proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi], next_weight=layer.out_proj)
             qkv, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
@@ -327,17 +362,17 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
             ai += 1
         r, rparts = row_parallel(mixed, layer.out_proj, layer.gate_up if layer.experts is None else after(li))
         if layer.experts is not None:
-            x, hrows = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts, rows_out=True, packed_out=False)
+            x, hrows = norm(x, r, layer.post_norm, partials=rparts, rows_out=True, packed_out=False)
             pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf, ep), None
             continue
-        x, h = lane_glue.norm_xs(x, r, layer.post_norm, c.eps, group=g, partials=rparts)
+        x, h = norm(x, r, layer.post_norm, partials=rparts)
         gu = lane_matmul(h, layer.gate_up, out=mlp_in, next_weight=layer.down)
         act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)
         pending, parts = row_parallel(act, layer.down, after(li))
     if not full_logits:
-        _, hrows = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, rows_out=True, packed_out=False, partials=parts)
+        _, hrows = norm(x, pending, w.norm, rows_out=True, packed_out=False, partials=parts)
         return hrows, rec
-    _, h = lane_glue.norm_xs(x, pending, w.norm, c.eps, group=g, partials=parts)
+    _, h = norm(x, pending, w.norm, partials=parts)
     return lane_matmul(h, w.head), rec
 
 

@@ -140,6 +140,17 @@ def lane_sdpa(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, s
                           kv.table, seq_lens, seq_start, nkeys, scale=scale, max_window=t, max_chunks=chunks_for(l))
 
 
+def lane_tree_sdpa(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, scale: float, parents) -> torch.Tensor:
+    """The reference's tree form (``lane_attention.lane_tree_sdpa``, ``:462-518``) for the windows this library
+    verifies: ``parents`` must describe a chain ([-1, 0, 1, ...]), in which case row t sees the prefix and rows
+    0..t and the call is ``lane_sdpa``; a branching tree raises ``ValueError`` (chains only)."""
+
+    parents = [int(p) for p in parents]
+    if len(parents) != queries.shape[0] or any(p != i - 1 for i, p in enumerate(parents)):
+        raise ValueError("lane_tree_sdpa: only chain windows are supported (parents must be [-1, 0, 1, ...])")
+    return lane_sdpa(queries, keys, values, scale)
+
+
 def kv_commit(k_new: torch.Tensor, v_new: torch.Tensor, kv: PagedKV, seq_lens: torch.Tensor, seq_start: torch.Tensor,
               keep: torch.Tensor) -> None:
     """Write the first keep[s] window rows of every sequence into its pages at positions seq_lens[s]..,
@@ -153,4 +164,4 @@ def kv_commit(k_new: torch.Tensor, v_new: torch.Tensor, kv: PagedKV, seq_lens: t
                    "kv_commit")
 
 
-__all__ = ["PAGE", "chunks_for", "PagedKV", "kv_commit", "lane_attention", "lane_sdpa", "scratch_bytes"]
+__all__ = ["PAGE", "chunks_for", "lane_tree_sdpa", "PagedKV", "kv_commit", "lane_attention", "lane_sdpa", "scratch_bytes"]

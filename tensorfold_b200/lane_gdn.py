@@ -94,6 +94,33 @@ def gdn_mixer(qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tens
     return (packed, rows) if rows_out else packed
 
 
+class LaneGDNCache:
+    """Many lanes forked from one committed state, advanced one position at a time (reference:
+    ``LaneGDNCache.step``, ``kernels/qwen/dense/v1/lane_gdn.py:377-450``). The reference keeps the shared
+    state S0 plus a per-lane history; here every lane owns its fp32 state (Hv x Dv x Dk, 64 KB a head: HBM
+    is not the scarce resource on this machine) and a step is the chain kernel over one-row windows, so a
+    lane's outputs have the bits of the serial recurrence."""
+
+    def __init__(self, s0: torch.Tensor, lanes: int):
+        if s0.dim() != 3 or s0.dtype != torch.float32 or lanes < 1:
+            raise ValueError("LaneGDNCache: s0 must be an fp32 (Hv, Dv, Dk) state")
+        _lib.need_cuda(s0)
+        self.lanes = lanes
+        self.state = s0.unsqueeze(0).repeat(lanes, 1, 1, 1).contiguous()
+        self.t = 0
+        self._starts = torch.arange(lanes + 1, dtype=torch.int32, device=s0.device)
+
+    def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_g: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+        """One position for every lane. q, k: [N, Hk, Dk]; v: [N, Hv, Dv]; log_g, beta: [N, Hv] -> y [N, Hv, Dv]."""
+
+        if q.shape[0] != self.lanes:
+            raise ValueError(f"LaneGDNCache.step: {self.lanes} lanes, got {q.shape[0]} rows")
+        y = gated_delta_chain(q.contiguous(), k.contiguous(), v.contiguous(), torch.exp(log_g.float()).contiguous(),
+                              beta.float().contiguous(), self.state, self._starts, state_out=self.state)
+        self.t += 1
+        return y
+
+
 def gated_delta_tree(q, k, v, g, beta, state, parents) -> torch.Tensor:
     """Reference signature for one sequence: ``parents`` must describe a chain."""
 
@@ -141,4 +168,4 @@ def conv_commit(qkv: torch.Tensor, conv_state: torch.Tensor, seq_start: torch.Te
                    "conv_commit")
 
 
-__all__ = ["chain_parents", "conv_commit", "gated_delta_chain", "gdn_mixer", "gated_delta_tree", "replay", "replay_path"]
+__all__ = ["LaneGDNCache", "chain_parents", "conv_commit", "gated_delta_chain", "gdn_mixer", "gated_delta_tree", "replay", "replay_path"]

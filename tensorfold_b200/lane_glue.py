@@ -31,13 +31,15 @@ def _bf16(*tensors):
 
 def norm_xs(hidden: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float, *, group: int = 64,
             partials: torch.Tensor | None = None, rows_out: bool = False, packed_out: bool = True,
-            out: Packed | None = None, h_out: torch.Tensor | None = None):
+            out: Packed | None = None, h_out: torch.Tensor | None = None, peer=None):
     """(h, x): h = hidden + residual (hidden itself when there is no residual), x = RMSNorm(h) * weight.
 
     ``residual`` is bf16 (M, D), or ``partials`` holds a row-parallel projection's fp32 per-rank
     outputs (ranks, M, D) that are added in rank order and rounded once. ``x`` is returned packed for
     the next matmul (``packed_out``) and/or as plain rows (``rows_out``): (h, packed), (h, rows) or
-    (h, packed, rows). Reference: ``lane_glue.norm_xs`` / ``glue.add_rmsnorm``.
+    (h, packed, rows). ``peer``: a ``distributed.RankGroup`` with the fused exchange: the addend is the
+    rank-ordered sum of the partials the ranks' ``lane_matmul(..., peer=...)`` calls stored in this rank's
+    exchange buffer. Reference: ``lane_glue.norm_xs`` / ``glue.add_rmsnorm``.
     """
 
     _bf16(hidden, residual, weight)
@@ -54,17 +56,24 @@ def norm_xs(hidden: torch.Tensor, residual: torch.Tensor | None, weight: torch.T
         nparts, pstride = partials.shape[0], m * d
     if residual is not None:
         residual = residual.contiguous()
-    has_res = residual is not None or nparts > 0
+    if peer is not None and (residual is not None or nparts > 0):
+        raise ValueError("norm_xs: a peer exchange excludes a residual and gathered partials")
+    has_res = residual is not None or nparts > 0 or peer is not None
     if has_res and h_out is None:
         h_out = torch.empty_like(hidden)
     h = h_out if has_res else hidden
     packed = (out if out is not None else new_packed(m, d, group, hidden.device)) if packed_out else None
     rows = torch.empty_like(hidden) if rows_out else None
     with torch.cuda.device(hidden.device):
-        _lib.check(_lib.load().tf_norm_xs(hidden.data_ptr(), _lib.ptr(residual), _lib.ptr(partials), nparts, pstride,
-                                          weight.data_ptr(), _lib.ptr(h_out) if has_res else None, _lib.ptr(rows),
-                                          packed.data.data_ptr() if packed else None, m, d, group, float(eps),
-                                          _lib.stream()), "norm_xs")
+        if peer is not None:
+            _, slot_bytes, seq, tickets, mine = peer.peer_args()
+        else:
+            slot_bytes, seq, tickets, mine = 0, None, None, None
+        _lib.check(_lib.load().tf_norm_xs_peer(hidden.data_ptr(), _lib.ptr(residual), _lib.ptr(partials), nparts, pstride,
+                                               weight.data_ptr(), _lib.ptr(h_out) if has_res else None, _lib.ptr(rows),
+                                               packed.data.data_ptr() if packed else None, m, d, group, float(eps),
+                                               mine, slot_bytes, seq, tickets, peer.world if peer is not None else 0,
+                                               _lib.status(hidden.device).word.data_ptr(), _lib.stream()), "norm_xs")
     if packed_out and rows_out:
         return h, packed, rows
     return h, (packed if packed_out else rows)

@@ -42,7 +42,8 @@ class ExpertGroup:
             raise ValueError(f"{experts} experts do not split over {self.world} ranks")
         self.per = experts // self.world
         total, slots = experts + (1 if shared else 0), top_k + (1 if shared else 0)
-        self.slot_bytes = _lib.load().tf_moe_max_problems(max_rows, slots, total) * 8 * hidden * 8
+        lib = _lib.load()
+        self.slot_bytes = (lib.tf_moe_slot_bytes(lib.tf_moe_max_problems(max_rows, slots, total), hidden) + 255) // 256 * 256
         self.buf = symm_mem.empty(2 * self.slot_bytes, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
@@ -188,15 +189,15 @@ def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: Experts, buf: MoEBuffers
             _lib.check(lib.tf_moe_combine(buf.y.data_ptr(), buf.pair_loc.data_ptr(), buf.wts.data_ptr(), buf.slots,
                                           buf.out.data_ptr(), rows, d, s), "moe combine")
         else:
-            if buf.max_probs * 8 * d * 8 > ep.slot_bytes:
+            if lib.tf_moe_slot_bytes(buf.max_probs, d) > ep.slot_bytes:
                 raise ValueError("moe: the expert group's exchange buffer is too small for these buffers")
-            slot_off = (ep.count & 1) * ep.slot_bytes
             ep.count += 1
             _lib.check(lib.tf_moe_push(buf.y.data_ptr(), buf.prob_sel.data_ptr(), buf.sel_count.data_ptr(), buf.max_probs, d,
-                                       ep.handle.buffer_ptrs_dev, slot_off, ep.world, ep.state[0:1].data_ptr(), s), "moe push")
-            _lib.check(lib.tf_moe_combine_peer(ep.buf.data_ptr() + slot_off, buf.pair_loc.data_ptr(), buf.wts.data_ptr(), buf.slots,
-                                               buf.out.data_ptr(), rows, d, ep.state[0:1].data_ptr(), ep.state[1:2].data_ptr(),
-                                               st.word.data_ptr(), s), "moe combine (peer)")
+                                       ep.handle.buffer_ptrs_dev, ep.slot_bytes, ep.rank, ep.world, ep.state[0:1].data_ptr(), s),
+                       "moe push")
+            _lib.check(lib.tf_moe_combine_peer(ep.buf.data_ptr(), ep.slot_bytes, buf.pair_loc.data_ptr(), buf.wts.data_ptr(),
+                                               buf.slots, buf.out.data_ptr(), rows, d, ep.world, ep.state[0:1].data_ptr(),
+                                               ep.state[1:2].data_ptr(), st.word.data_ptr(), s), "moe combine (peer)")
     return buf.out
 
 

@@ -187,18 +187,45 @@ def scratch_for(device: torch.device) -> torch.Tensor:
     return buf
 
 
-def lane_matmul(x: torch.Tensor | Packed, weight: QWeight, *, f32: bool = False,
-                out: torch.Tensor | None = None, next_weight: QWeight | None = None) -> torch.Tensor:
+_tiled_cache: dict[tuple, QWeight] = {}
+
+
+def _as_qweight(weight, scales, biases) -> QWeight:
+    """The reference's call shape: stored words + scales + biases. Tiled once per (words, scales, biases)
+    storage and remembered, as the reference remembers its regrouped weights."""
+
+    key = (weight.data_ptr(), scales.data_ptr(), biases.data_ptr(), tuple(weight.shape))
+    q = _tiled_cache.get(key)
+    if q is None:
+        q = _tiled_cache[key] = tile_weight(weight, scales, biases)
+    return q
+
+
+def lane_matmul(x: torch.Tensor | Packed, weight, scales: torch.Tensor | None = None, biases: torch.Tensor | None = None, *,
+                xs: torch.Tensor | None = None, sk: int | None = None, f32: bool = False,
+                out: torch.Tensor | None = None, next_weight: QWeight | None = None, peer=None) -> torch.Tensor:
     """x (..., K) bf16 — or rows already ``Packed`` by the producing kernel — times the 4-bit
     ``weight`` (N, K) transposed -> (..., N) bf16.
 
+    ``weight`` is a ``QWeight`` (tiled once by ``tile_weight``) or, in the reference's call shape
+    ``lane_matmul(x, weight, scales, biases, xs=..., sk=...)``, the stored (N, K/8) words with their scales
+    and biases (tiled on first use). ``xs`` (the input's group sums) is accepted for that call shape and not
+    needed: packing forms the sums; ``sk`` must be None or the shape's own ``split_k``.
     ``f32``: return the unrounded fp32 sums (a tensor-parallel rank's partial). More than
     ``MAX_ROWS`` rows run as several launches; a row's bits do not depend on which launch it rides in.
     ``next_weight``: the weight of the matmul launched next on this stream; its first bytes are pulled
-    into L2 while this one finishes (a hint only).
+    into L2 while this one finishes (a hint only). ``peer``: a ``distributed.RankGroup`` with the fused
+    exchange: the fp32 sums go straight into every rank's exchange buffer (nothing is returned; the next
+    ``norm_xs(..., peer=...)`` adds the ranks' partials).
     """
 
     lib = _lib.load()
+    if not isinstance(weight, QWeight):
+        if scales is None or biases is None:
+            raise ValueError("lane_matmul: stored words need their scales and biases")
+        weight = _as_qweight(weight, scales, biases)
+    if sk is not None and sk != split_k(weight.n, weight.k):
+        raise ValueError(f"lane_matmul: the K schedule is fixed by the shape (split_k = {split_k(weight.n, weight.k)}), got sk={sk}")
     if isinstance(x, Packed):
         if x.k != weight.k or x.group != weight.group:
             raise ValueError(f"lane_matmul: packed rows (K={x.k}, group {x.group}) do not match the weight "
@@ -218,6 +245,19 @@ def lane_matmul(x: torch.Tensor | Packed, weight: QWeight, *, f32: bool = False,
         if m < 1:
             raise ValueError("lane_matmul: needs at least one row")
         chunks = [pack_rows(x2[r0:r0 + MAX_ROWS], weight.group) for r0 in range(0, m, MAX_ROWS)]
+    if peer is not None:
+        if len(chunks) != 1:
+            raise ValueError("lane_matmul: a tensor-parallel partial is at most MAX_ROWS rows")
+        bufs, slot_bytes, seq, _, _ = peer.peer_args()
+        nw = next_weight
+        with torch.cuda.device(dev):
+            scratch = scratch_for(dev)
+            _lib.check(lib.tf_qmm_peer(chunks[0].data.data_ptr(), weight.tiled.data_ptr(), scratch.data_ptr(), scratch.numel(), m,
+                                       weight.n, weight.k, weight.group, bufs, slot_bytes, seq, peer.rank, peer.world,
+                                       nw.tiled.data_ptr() if nw is not None else None, nw.n if nw is not None else 0,
+                                       nw.k if nw is not None else 0, nw.group if nw is not None else 0,
+                                       _lib.status(dev).word.data_ptr(), _lib.stream()), "lane_matmul (peer)")
+        return None
     dtype = torch.float32 if f32 else torch.bfloat16
     if out is None:
         out = torch.empty((m, weight.n), dtype=dtype, device=dev)

@@ -64,3 +64,39 @@ def test_drafted_tokens_equal_serial_tokens(setup, sampled):
     st, pending4 = fresh()
     copied = decode.draft_decode(w, st, prompts, pending4, count, sampling, max_rows=8)
     assert copied.sha256() == serial.sha256()
+
+
+def test_snapshot_restore_and_generate(setup):
+    """``State.snapshot`` / ``restore`` (reference: families/qwen4_exp/cuda/forward.py:200-222) bring the sequences
+    back bit for bit, refuse a snapshot of other kernels, and ``Engine.generate`` (the contract of cuda/server.py:9-15)
+    emits the serial tokens, streams them through ``on_tokens`` and reuses a committed prefix."""
+
+    decode, F, Sampling, w, prompts = setup
+    sampling = Sampling(seed=3, temperature=0.7, top_k=20, top_p=0.9)
+    st = F.State(w, len(prompts), 256)
+    pending = decode.prefill(w, st, prompts, sampling)
+    snap = st.snapshot()
+    first = decode.serial_decode(w, st, pending, 10, sampling)
+    st.restore(snap)
+    again = decode.serial_decode(w, st, pending, 10, sampling)
+    assert first.tokens == again.tokens
+    with pytest.raises(ValueError):
+        st.restore(dict(snap, kernels="another build"))
+
+    # one request at a time through the engine
+    st1 = F.State(w, 1, 256)
+    p1 = decode.prefill(w, st1, [prompts[1]], sampling)
+    want = decode.serial_decode(w, st1, p1, 20, sampling).tokens[0]
+    eng = decode.Engine(w, max_context=256)
+    seen = []
+    got = eng.generate(prompts[1], 20, sampling, on_tokens=lambda new: seen.extend(new) or False)
+    assert got["tokens"] == want and seen == want and got["prompt_tokens"] == len(prompts[1])
+    # a follow-up whose prompt extends the finished exchange reuses the committed prefix
+    longer = prompts[1] + want[:12]
+    st2 = F.State(w, 1, 256)
+    p2 = decode.prefill(w, st2, [longer], sampling)
+    want2 = decode.serial_decode(w, st2, p2, 8, sampling).tokens[0]
+    assert eng.generate(longer, 8, sampling)["tokens"] == want2
+    # stopping early through the callback
+    short = decode.Engine(w, max_context=256).generate(prompts[0], 20, sampling, on_tokens=lambda new: True)
+    assert len(short["tokens"]) == 1

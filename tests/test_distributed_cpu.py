@@ -100,7 +100,7 @@ def test_split_vocabulary_candidates_contain_the_whole_vocabulary_draw():
     midx, mval = H.merge_candidates(torch.stack(idx), torch.stack(val), 28)
     wi, wv = O.topk_rows(logits, 28)
     assert np.array_equal(midx.numpy(), wi) and np.array_equal(mval.numpy(), wv)
-    assert S.choose_rows(mval.numpy(), midx.numpy(), positions, s) == whole
+    assert O.choose_rows(mval.numpy(), midx.numpy(), positions, O.Sampling(seed=77, top_k=20, top_p=0.9)) == whole
 
 
 def test_split_model_shards_reassemble_into_the_stored_model():
@@ -185,3 +185,131 @@ def test_checkpoint_roundtrip_keeps_every_array(tmp_path):
     st_.save_file(tensors, str(tmp_path / "model.safetensors"))
     with pytest.raises(ValueError):
         weights.load(tmp_path)
+
+
+# ---- failure handling on the host: nothing here touches a GPU ------------------------------------------
+
+def _settings_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        tp = D.RankGroup()
+        tp.check_settings({"max_rows": 8, "split_head": True})           # equal everywhere: passes
+        try:
+            tp.check_settings({"max_rows": 8 if rank == 0 else 16, "split_head": True})
+            out[rank] = "started"
+        except RuntimeError as exc:
+            out[rank] = str(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def _port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_ranks_with_different_settings_refuse_to_start():
+    """After the reference's start-up check (families/qwen3_5/cuda/engine.py:54-62, tests/cuda/test_flashnext_tp.py:436-457)."""
+
+    out = mp.Manager().dict()
+    mp.spawn(_settings_worker, args=(2, _port(), out), nprocs=2, join=True)
+    for rank in range(2):
+        assert "different settings" in out[rank] and "max_rows" in out[rank], out[rank]
+
+
+def _absent_worker(rank, world, port, out):
+    import datetime
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=3))
+    tp = D.RankGroup()
+    if rank == 1:
+        out[rank] = "left before the exchange"       # a rank that never arrives at the collective
+        return
+    try:
+        tp.gather_partials(torch.ones((2, 8)))
+        out[rank] = "gathered"
+    except Exception as exc:                          # the short group timeout ends the wait with an error
+        out[rank] = f"error: {type(exc).__name__}"
+
+
+def test_a_rank_that_never_arrives_ends_the_others_wait_with_an_error():
+    out = mp.Manager().dict()
+    mp.spawn(_absent_worker, args=(2, _port(), out), nprocs=2, join=True)
+    assert out[1] == "left before the exchange"
+    assert out[0].startswith("error"), out[0]
+
+
+def _raising_worker(rank, world, port, out):
+    import datetime
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=3))
+    tp = D.RankGroup()
+    first = tp.gather_partials(torch.full((1, 8), float(rank)))
+    out[f"first{rank}"] = first[:, 0, 0].tolist()
+    if rank == 1:
+        raise ValueError("rank 1 fails between two steps")
+    try:
+        tp.gather_partials(torch.ones((1, 8)))
+        out[rank] = "gathered"
+    except Exception as exc:
+        out[rank] = f"error: {type(exc).__name__}"
+
+
+def test_a_rank_that_raises_between_steps_is_seen_by_the_others():
+    out = mp.Manager().dict()
+    with pytest.raises(Exception):                    # the failing rank's exception reaches the launcher
+        mp.spawn(_raising_worker, args=(2, _port(), out), nprocs=2, join=True)
+    assert out["first0"] == [0.0, 1.0]               # the step before the failure completed on rank 0
+
+
+# ---- the expert-parallel exchange's slot-reuse rule, as a model ------------------------------------------------
+def _simulate_expert_exchange(world, exchanges, presence, seed):
+    """Ranks as state machines under a random scheduler. Exchange n: a rank pushes the results of the problems
+    it owns (possibly none) into slot n & 1 of every rank's buffer, plus - with ``presence`` - its presence cell;
+    its combine then needs the data of all owners and, with ``presence``, every rank's cell, and only then
+    advances its exchange number. Returns the first overwrite of a slot that its reader has not finished with."""
+
+    import random
+
+    rng = random.Random(seed)
+    owners = [[r for r in range(world) if rng.random() < 0.4] for _ in range(exchanges + 1)]     # owners[n]; may be empty
+    done = [0] * world                           # exchanges a rank has completed
+    pushed = [0] * world                         # exchanges a rank has pushed
+    data = [[{} for _ in range(2)] for _ in range(world)]       # data[rank][slot][owner] = n
+    cell = [[{} for _ in range(2)] for _ in range(world)]
+    while min(done) < exchanges:
+        r = rng.randrange(world)
+        n = done[r] + 1
+        if n > exchanges:
+            continue
+        if pushed[r] < n:                        # push n
+            for peer in range(world):
+                if presence:
+                    cell[peer][n & 1][r] = n
+                if r in owners[n]:
+                    if done[peer] < n - 2:       # peer has not finished the exchange that used this slot before
+                        return (r, peer, n)
+                    data[peer][n & 1][r] = n
+            pushed[r] = n
+        elif all(data[r][n & 1].get(o) == n for o in owners[n]) and \
+                (not presence or all(cell[r][n & 1].get(p) == n for p in range(world))):
+            done[r] = n                          # combine n passed
+    return None
+
+
+def test_presence_cells_keep_a_fast_rank_from_overwriting_a_slot_in_use():
+    for seed in range(200):
+        assert _simulate_expert_exchange(4, 40, True, seed) is None
+    # the model does find the overwrite when only data packets couple the ranks
+    assert any(_simulate_expert_exchange(4, 40, False, seed) is not None for seed in range(200))

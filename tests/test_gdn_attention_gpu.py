@@ -290,7 +290,7 @@ def test_keyed_sampling_matches_reference_fixture(lib):
 
     z = np.load(Path(__file__).parent / "golden" / "exact_sampling.npz")
     vals, ids, positions = z["vals"], z["ids"], z["positions"]
-    assert np.array_equal(S.uniform_rows(1234, positions[:8], ids[:8]), z["u"])
+    assert np.array_equal(O.uniform_rows(1234, positions[:8], ids[:8]), z["u"])
     for name, s in (("default", S.Sampling(seed=1234)), ("hot", S.Sampling(seed=99, temperature=1.7, top_k=10, top_p=0.8))):
         assert S.choose_rows(vals, ids, positions, s) == z["pick_" + name].tolist()
     # the device draw on logits rows whose top candidates are the fixture's rows
@@ -386,3 +386,35 @@ def test_gdn_lane_step_at_config_2_shape(lib):
     full = dev[5].clone()
     lane_gdn.replay(dev[1], dev[2], dev[3], dev[4], full, dev[6], torch.full((32,), 8, dtype=torch.int32).cuda())
     assert torch.equal(full.view(torch.int32), st.view(torch.int32)), "replay(8) == eight serial steps"
+
+
+def test_reference_call_shapes_tree_sdpa_and_gdn_cache(lib):
+    """``lane_tree_sdpa`` for chain parents is ``lane_sdpa`` and refuses a branching tree; ``LaneGDNCache.step``
+    advances every lane by one position with the bits of the chain kernel over the same rows."""
+
+    from tensorfold_b200 import lane_attention as LA, lane_gdn
+
+    gen = torch.Generator().manual_seed(8)
+    l, t, h, hk, d = 90, 4, 4, 2, 128
+    q = torch.randn((t, h, d), generator=gen).to(BF).cuda()
+    k = torch.randn((l, hk, d), generator=gen).to(BF).cuda()
+    v = torch.randn((l, hk, d), generator=gen).to(BF).cuda()
+    assert_same_bits(LA.lane_tree_sdpa(q, k, v, d ** -0.5, [-1, 0, 1, 2]), LA.lane_sdpa(q, k, v, d ** -0.5), "chain tree")
+    with pytest.raises(ValueError):
+        LA.lane_tree_sdpa(q, k, v, d ** -0.5, [-1, 0, 0, 1])
+
+    lanes, steps = 3, 4
+    qq, kk, vv, g, beta, state, _ = gdn_inputs(6, [steps] * lanes)
+    s0 = state[0].cuda()
+    cache = lane_gdn.LaneGDNCache(s0, lanes)
+    ys = []
+    for i in range(steps):
+        sel = torch.arange(lanes) * steps + i
+        ys.append(cache.step(qq[sel].cuda(), kk[sel].cuda(), vv[sel].cuda(), torch.log(g[sel]).cuda(), beta[sel].cuda()))
+    starts = torch.arange(0, lanes * steps + 1, steps, dtype=torch.int32).cuda()
+    # the chain kernel takes g itself; the cache takes log g and exponentiates: feed the chain the same values
+    gexp = torch.exp(torch.log(g).cuda().float())
+    want = lane_gdn.gated_delta_chain(qq.cuda(), kk.cuda(), vv.cuda(), gexp, beta.cuda(), s0.unsqueeze(0).repeat(lanes, 1, 1, 1).contiguous(), starts)
+    for i in range(steps):
+        sel = (torch.arange(lanes) * steps + i).cuda()
+        assert_same_bits(ys[i], want[sel], f"cache step {i}")

@@ -190,3 +190,41 @@ def test_embed(mods):
         ids = torch.tensor([0, 299, 17, 17, 123], dtype=torch.int32)
         out = glue.embed(ids.cuda(), q.words.cuda(), q.scales.cuda(), q.biases.cuda(), 512, group)
         assert_same_bits(out.cpu(), O.embed(ids, q.words, q.scales, q.biases, group), "embed is exact")
+
+
+def test_lane_fuse_stacks_and_reads_in_place(mods):
+    """The reference's lane_fuse entry points (tests/test_lane_fuse.py: stacked output == members side by side,
+    consumers read the stack in place): a stacked row has the bits of that row alone, every member's columns
+    are within the matmul tolerance of the member projected by itself, and gdn_post / mlp_act on the stacked
+    rows equal the kernels on separate tensors."""
+
+    from tensorfold_b200 import lane_fuse, lane_qmm
+
+    glue, qmm = mods
+    gen = torch.Generator().manual_seed(9)
+    nv, dv, d = 4, 128, 512
+    layer = {"z": O.random_q4(gen, nv * dv, d, 64), "b": O.random_q4(gen, nv, d, 64), "a": O.random_q4(gen, nv, d, 64),
+             "gate": O.random_q4(gen, 256, d, 64), "up": O.random_q4(gen, 256, d, 64)}
+    model = {"config": O.Config(hidden=d, intermediate=256, layers=1, heads=2, kv_heads=1, head_dim=128, vocab=64, k_heads=2,
+                                v_heads=nv, dk=128, dv=128), "layers": [layer]}
+    assert lane_fuse.attn_kv(layer, torch.zeros((1, d), dtype=BF).cuda()) is None          # nothing stacked yet
+    assert lane_fuse.build(model) == {"zba": 1, "kv": 0, "gu": 1}
+    assert lane_fuse.stats(model)["groups"] == {"zba": 1, "kv": 0, "gu": 1}
+    x = torch.randn((5, d), generator=gen).to(BF).cuda()
+    zba = lane_fuse.gdn_in(layer, x)
+    assert zba.shape == (5, nv * dv + 2 * nv)
+    assert_same_bits(lane_fuse.gdn_in(layer, x[2:3]), zba[2:3], "stacked row alone")
+    zq = layer["z"]
+    z_alone = qmm.lane_matmul(x, qmm.tile_weight(zq.words.cuda(), zq.scales.cuda(), zq.biases.cuda(), 64))
+    assert_close(zba[:, :nv * dv], z_alone.cpu(), "z member of the stack")
+    y = torch.randn((5, nv, dv), generator=gen).to(BF).cuda()
+    w = (1 + 0.05 * torch.randn(dv, generator=gen)).to(BF).cuda()
+    a = lane_fuse.gdn_post(y, zba, w, 1e-6)
+    b = glue.gdn_post(y, zba[:, :nv * dv].contiguous(), w, 1e-6)
+    assert torch.equal(a.data, b.data)
+    gu = lane_fuse.mlp_gate_up(layer, x)
+    a = lane_fuse.mlp_act(gu)
+    b = glue.mlp_act(gu[:, :256].contiguous(), gu[:, 256:].contiguous())
+    assert torch.equal(a.data, b.data)
+    lane_fuse.clear(model)
+    assert lane_fuse.gdn_in(layer, x) is None

@@ -124,6 +124,20 @@ def test_rows_packed_by_the_caller_and_launch_numbers_in_step(qmm):
     assert int(scratch[:16384].view(torch.int32).abs().sum()) == 0         # the prefill kernel's ticket words
 
 
+def test_reference_call_shape_with_stored_weights(qmm):
+    """``lane_matmul(x, weight, scales, biases, xs=..., sk=...)`` as the reference calls it (families/qwen3_5/cuda/qmm.py:117-144)."""
+
+    x, words, scales, biases = make(1024, 5120, 64, seed=12, rows=8)
+    wd, sd, bd = words.cuda(), scales.cuda(), biases.cuda()
+    tiled = qmm.lane_matmul(x.cuda(), qmm.tile_weight(wd, sd, bd, 64))
+    xs = qmm.group_sums(x.cuda())
+    assert_same_bits(qmm.lane_matmul(x.cuda(), wd, sd, bd, xs=xs, sk=qmm.split_k(1024, 5120)), tiled, "stored call shape")
+    with pytest.raises(ValueError):
+        qmm.lane_matmul(x.cuda(), wd, sd, bd, sk=qmm.split_k(1024, 5120) + 1)
+    with pytest.raises(ValueError):
+        qmm.lane_matmul(x.cuda(), wd)
+
+
 def test_wrong_arguments_raise(qmm):
     x, words, scales, biases = make(64, 128, 64, seed=2)
     q = qmm.tile_weight(words.cuda(), scales.cuda(), biases.cuda(), 64)

@@ -76,12 +76,21 @@ def main():
         full1 = torch.cat(parts1, dim=-1).float().flatten()
         r = ref.float().flatten()
         cos = float(torch.dot(full1, r) / (full1.norm() * r.norm()))
-    flags = torch.tensor([int(same), int(head_ok)], device=dev)
+    # the exchange fused into the matmul epilogue and the norm kernel carries the bits of the plain
+    # all-gather + rank-ordered sum (same order, one rounding)
+    fused_ok = True
+    if tp.fused:
+        tp2 = distributed.RankGroup(exchange="nccl")
+        st3 = F.State(w, 1, 256, dev)
+        l1n, _ = F.tree_forward(w, torch.tensor(tokens[:12], dtype=torch.int32, device=dev), [-1] + list(range(11)), st3, tp=tp2)
+        fused_ok = bool(torch.equal(l1n.view(torch.int16), l1.view(torch.int16)))
+    flags = torch.tensor([int(same), int(head_ok), int(fused_ok)], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
         from tensorfold_b200 import _lib
         _lib.status(dev).raise_if_set()
-        print(f"TP_RESULT world={world} window_equals_serial={int(flags[0])} head_ok={int(flags[1])} cos_vs_one_gpu={cos:.6f}", flush=True)
+        print(f"TP_RESULT world={world} window_equals_serial={int(flags[0])} head_ok={int(flags[1])} cos_vs_one_gpu={cos:.6f} "
+              f"fused_equals_gathered={int(flags[2])} exchange={tp.exchange}", flush=True)
     dist.destroy_process_group()
 
 
