@@ -139,6 +139,114 @@ def cpu_reference(args, rows: int):
                       f"{rows} rows, scaled to 48 + 16 layers + head by weight count"}
 
 
+def reference_gpu(args, rows: int):
+    """The reference's own CUDA lane path (its Triton kernels and JIT-built GDN kernel, copied unmodified into
+    ``oracle/_ref`` by ``oracle/make_ref.py``) timed on this GPU: the tiled lane matmul at the headline shape, and one
+    verify window of the 64-layer 27B-class model through its ``forward.tree_forward`` as its engine calls it (eager).
+    Random weights in its stored layout, regrouped by its own ``qmm_fast.prepare``; context set directly (random
+    K/V rows, zero recurrent state). Returns {"unavailable": why} where that path cannot run."""
+
+    ref_dir = ROOT / "oracle" / "_ref"
+    if not (ref_dir / "tensorfold").is_dir():
+        return {"unavailable": "oracle/_ref is absent (made by oracle/make_ref.py where the reference checkout exists)"}
+    try:
+        import torch
+
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device"}
+        sys.path.insert(0, str(ref_dir))
+        from tensorfold.families.qwen3_5.cuda import forward as RF, qmm_fast
+        from tensorfold.families.qwen3_5.cuda.weights import Attention, Config, GDN, Layer, QLinear, Weights
+    except Exception as exc:
+        return {"unavailable": f"the reference's CUDA path does not import here: {type(exc).__name__}: {exc}"}
+    try:
+        dev = torch.device("cuda", 0)
+        gen = torch.Generator(device=dev).manual_seed(1)
+        bf = torch.bfloat16
+
+        def ql(n, k):
+            words = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, dtype=torch.int64, device=dev).to(torch.int32)
+            sc = ((torch.rand((n, k // 64), generator=gen, device=dev) / 8 + 1 / 64) * (4.0 / k ** 0.5)).to(bf)
+            return QLinear(words, sc, (-7.5 * sc.float()).to(bf))
+
+        def time_us(fn, n):
+            for _ in range(3):
+                fn(0)
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(n):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            return 1000.0 * e0.elapsed_time(e1) / n
+
+        out = {"kind": "the reference's Triton lane kernels on this GPU, called through its own Python API"}
+        # the headline matmul: four weight copies rotated through so every launch streams from HBM
+        n, k = 17408, 5120
+        x = torch.randn((rows, k), device=dev, generator=gen).to(bf)
+        copies = [qmm_fast.tile(ql(n, k)) for _ in range(4)]
+        eager = time_us(lambda i: qmm_fast.matmul(x, copies[i % 4]), 40)
+        out["qmm_17408x5120"] = {"rows": rows, "eager_us_per_launch": eager}
+        try:
+            side, graph = torch.cuda.Stream(dev), torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                qmm_fast.matmul(x, copies[0])
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for q in copies:
+                        qmm_fast.matmul(x, q)
+            torch.cuda.synchronize(dev)
+            out["qmm_17408x5120"]["graph_us_per_launch"] = time_us(lambda i: graph.replay(), 10) / 4
+        except Exception as exc:
+            out["qmm_17408x5120"]["graph_us_per_launch"] = None
+            out["qmm_17408x5120"]["graph_note"] = f"not capturable: {type(exc).__name__}"
+            torch.cuda.synchronize(dev)
+        alg = n * k // 2 + n * (k // 64) * 4 + rows * k * 2 + rows * n * 2
+        best = out["qmm_17408x5120"].get("graph_us_per_launch") or eager
+        out["qmm_17408x5120"]["achieved_gbs"] = alg / best / 1e3
+        del copies
+        # the whole verify window
+        c = dict(hidden=5120, intermediate=17408, layers=args.layers, heads=24, kv_heads=4, head_dim=256, vocab=248320, k_heads=16,
+                 v_heads=32, dk=128, dv=128)
+        cfg = Config(**c, conv_kernel=4, interval=4, eps=1e-6, rope_dims=64, rope_theta=1e7, eos=(0,))
+        kd, vd, h = 16 * 128, 32 * 128, 5120
+
+        def norm(m):
+            return (1 + 0.05 * torch.randn(m, generator=gen, device=dev)).to(bf)
+        layers = []
+        for i in range(cfg.layers):
+            if cfg.is_linear(i):
+                gdn = GDN(ql(2 * kd + vd, h), ql(vd, h), ql(32, h), ql(32, h), ql(h, vd),
+                          (0.3 * torch.randn((2 * kd + vd, 4), generator=gen, device=dev)).to(bf),
+                          0.5 * torch.randn(32, generator=gen, device=dev), 0.5 * torch.randn(32, generator=gen, device=dev), norm(128))
+                layers.append(Layer(True, norm(h), norm(h), gdn, None, ql(17408, h), ql(17408, h), ql(h, 17408)))
+            else:
+                att = Attention(ql(24 * 512, h), ql(4 * 256, h), ql(4 * 256, h), ql(h, 24 * 256), norm(256), norm(256))
+                layers.append(Layer(False, norm(h), norm(h), None, att, ql(17408, h), ql(17408, h), ql(h, 17408)))
+        half = 32
+        inv_freq = (1e7 ** (-torch.arange(0, half, dtype=torch.float64) / half)).to(torch.float32).to(dev)
+        w = Weights(cfg, ql(cfg.vocab, h), layers, norm(h), ql(cfg.vocab, h), inv_freq)
+        qmm_fast.prepare(w)
+        st = RF.State(w)
+        st.pos = args.ctx
+        for i, layer in enumerate(w.layers):
+            if not layer.linear:
+                st.kv[i] = tuple(torch.randn((args.ctx + 64, 4, 256), device=dev, generator=gen).to(bf) for _ in range(2))
+        width = args.width
+        tokens = torch.randint(0, cfg.vocab, (width,), generator=gen, device=dev, dtype=torch.int32)
+        parents = [-1] + list(range(width - 1))
+        ms = time_us(lambda i: RF.tree_forward(w, tokens, parents, st), max(args.steps, 5)) / 1000.0
+        out["forward"] = {"ms_per_window": ms, "rows_per_s": width / ms * 1000.0, "rows": width, "context": args.ctx, "layers": cfg.layers,
+                          "note": "one sequence; eager launches, as the reference's engine issues them; synthetic context"}
+        return out
+    except Exception as exc:
+        return {"unavailable": f"the reference's CUDA path failed here: {type(exc).__name__}: {str(exc)[:200]}"}
+    finally:
+        if str(ref_dir) in sys.path:
+            sys.path.remove(str(ref_dir))
+
+
 def only_qmm(args, dev):
     """The lane matmul alone: --copies weights of --shape rotated through so that every launch streams
     from HBM; CUDA-event time per launch, algorithmic bytes, fraction of the measured copy bandwidth."""
@@ -170,6 +278,7 @@ def only_qmm(args, dev):
     for q in ws:
         run(q)
     torch.cuda.synchronize(dev)
+    # eager: launches back to back from the host (includes launch gaps)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = max(args.steps, 1) * args.copies
     e0.record()
@@ -177,15 +286,155 @@ def only_qmm(args, dev):
         run(ws[i % args.copies])
     e1.record()
     torch.cuda.synchronize(dev)
+    eager_us = 1000.0 * e0.elapsed_time(e1) / launches
+    # graph: the same rotation captured once and replayed, as the forward issues it
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        run(ws[0])
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for q in ws:
+                run(q)
+    torch.cuda.synchronize(dev)
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    reps = max(args.steps, 1)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
     _lib.status(dev).raise_if_set()
-    us = 1000.0 * e0.elapsed_time(e1) / launches
+    us = 1000.0 * e0.elapsed_time(e1) / (reps * args.copies)
     kg = k // group
     alg = n * k // 2 + n * kg * 4 + rows * k * 2 + rows * kg * 4 + rows * n * 2
     peak, kind = peaks()
     flops = 2.0 * rows * n * k
-    print(json.dumps({"only": args.only, "tflops": flops / us / 1e6, "shape": [n, k], "rows": rows, "launches": launches, "us_per_launch": us,
-                      "note": "eager launches back to back (includes launch gaps); the graph-replayed figure is in the main line",
+    print(json.dumps({"only": args.only, "tflops": flops / us / 1e6, "shape": [n, k], "rows": rows, "launches": reps * args.copies,
+                      "us_per_launch": us, "eager_us_per_launch": eager_us,
+                      "note": f"{args.copies} weight copies rotated through, captured in a CUDA graph and replayed; eager figure beside it",
                       "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
+
+
+def only_gdn(args, dev):
+    """The gated-DeltaNet lane step alone (conv1d + gates + recurrence + gated norm, one fused kernel per layer):
+    --seqs sequences x --width rows, 16 QK heads, 32 V heads, head dim 128, fp32 state N(0, 0.1) per layer;
+    --layers layers with their own state rotated through (32 sequences: 67 MB of state a layer), graph-replayed."""
+
+    import torch
+
+    from tensorfold_b200 import _lib, lane_gdn, lane_qmm
+
+    seqs, w, nk, nv, layers = args.seqs, args.width, 16, 32, min(args.layers, 12)
+    r, c = seqs * w, (2 * 16 + 32) * 128
+    gen = torch.Generator(device=dev).manual_seed(5)
+    proj = torch.randn((r, c + nv * 128 + 2 * nv), device=dev, generator=gen).to(torch.bfloat16)
+    qkv, z = proj[:, :c], proj[:, c:c + nv * 128]
+    bb, aa = proj[:, c + nv * 128:c + nv * 128 + nv], proj[:, c + nv * 128 + nv:]
+    conv_state = torch.randn((layers, seqs, 3, c), device=dev, generator=gen).to(torch.bfloat16)
+    conv_w = (0.3 * torch.randn((c, 4), device=dev, generator=gen)).to(torch.bfloat16)
+    a_log, dt = 0.5 * torch.randn(nv, device=dev, generator=gen), 0.5 * torch.randn(nv, device=dev, generator=gen)
+    nw = torch.ones(128, device=dev, dtype=torch.bfloat16)
+    state = 0.1 * torch.randn((layers, seqs, nv, 128, 128), device=dev, generator=gen)
+    starts = torch.arange(0, r + 1, w, dtype=torch.int32, device=dev)
+    rec = (torch.empty((r, nk, 128), device=dev, dtype=torch.bfloat16), torch.empty((r, nv, 128), device=dev, dtype=torch.bfloat16),
+           torch.empty((r, nv), device=dev), torch.empty((r, nv), device=dev))
+    out = lane_qmm.new_packed(r, nv * 128, 64, dev)
+
+    def layer(i):
+        lane_gdn.gdn_mixer(qkv, z, aa, bb, conv_state[i], conv_w, a_log, dt, nw, state[i], starts, nk=nk, nv=nv, eps=1e-6, group=64,
+                           record=rec, out=out)
+    for i in range(layers):
+        layer(i)
+    torch.cuda.synchronize(dev)
+    side, graph = torch.cuda.Stream(dev), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        layer(0)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(layers):
+                layer(i)
+    torch.cuda.synchronize(dev)
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(args.steps, 1)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    _lib.status(dev).raise_if_set()
+    us = 1000.0 * e0.elapsed_time(e1) / (reps * layers)
+    alg = seqs * nv * 128 * 128 * 4 + r * (c + nv * 128) * 2 + r * nv * 128 * 2      # state read (kept in place), rows in, rows out
+    peak, kind = peaks()
+    print(json.dumps({"only": "gdn", "seqs": seqs, "width": w, "layers_rotated": layers, "us_per_layer": us, "rows_per_s": r / us * 1e6,
+                      "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind,
+                      "note": "state is read once and not written back by the verify step (the accepted prefix is replayed at commit)"}))
+
+
+def only_attn(args, dev):
+    """Lane GQA attention alone at the 27B-class shape (24 Q heads, 4 KV heads, head dim 256, 16-token pages): --seqs
+    sequences x --width rows at context --ctx; 16 layers of KV rotated through, graph-replayed."""
+
+    import torch
+
+    from tensorfold_b200 import _lib, lane_attention as LA
+
+    seqs, w, ctx, h, hk, d = args.seqs, args.width, args.ctx, 24, 4, 256
+    layers = 16
+    while layers > 1 and layers * seqs * (ctx + w) * 2 * hk * d * 2 > (24 << 30):
+        layers //= 2
+    pages_per = -(-(ctx + w) // 16)
+    kv = LA.PagedKV(layers, seqs, seqs * pages_per, hk, d, pages_per, dev)
+    for s_ in range(seqs):
+        kv.reserve(s_, ctx + w)
+    kv.sync_table()
+    kv.k.normal_()
+    kv.v.normal_()
+    r = seqs * w
+    gen = torch.Generator(device=dev).manual_seed(9)
+    q = torch.randn((r, h, d), device=dev, generator=gen).to(torch.bfloat16)
+    kn = torch.randn((r, hk, d), device=dev, generator=gen).to(torch.bfloat16)
+    vn = torch.randn((r, hk, d), device=dev, generator=gen).to(torch.bfloat16)
+    lens = torch.full((seqs,), ctx, dtype=torch.int32, device=dev)
+    starts = torch.arange(0, r + 1, w, dtype=torch.int32, device=dev)
+    nkeys = torch.tensor([ctx + t + 1 for _ in range(seqs) for t in range(w)], dtype=torch.int32, device=dev)
+    ch = LA.chunks_for(ctx + w)
+    scratch = torch.empty(LA.scratch_bytes(r, h, d, ch), dtype=torch.uint8, device=dev)
+    out = torch.empty_like(q)
+
+    def layer(i):
+        LA.lane_attention(q, kn, vn, kv.k[i], kv.v[i], kv.table, lens, starts, nkeys, scale=d ** -0.5, max_window=w, max_chunks=ch,
+                          scratch=scratch, out=out)
+    for i in range(layers):
+        layer(i)
+    torch.cuda.synchronize(dev)
+    side, graph = torch.cuda.Stream(dev), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        layer(0)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(layers):
+                layer(i)
+    torch.cuda.synchronize(dev)
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(args.steps, 1)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    _lib.status(dev).raise_if_set()
+    us = 1000.0 * e0.elapsed_time(e1) / (reps * layers)
+    alg = seqs * (ctx + w) * 2 * hk * d * 2 + 2 * r * h * d * 2
+    peak, kind = peaks()
+    print(json.dumps({"only": "attn", "seqs": seqs, "width": w, "context": ctx, "layers_rotated": layers, "key_chunks": ch,
+                      "us_per_layer": us, "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak,
+                      "peak_kind": kind, "l2": "KV of the rotated layers exceeds L2" if layers * alg > (126 << 20) else "KV fits L2"}))
 
 
 def bench_moe(args, dev, rank=0, world=1):
@@ -308,14 +557,17 @@ def main():
     ap.add_argument("--width", type=int, default=8)
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-batch16", action="store_true", help="skip the extra 16-sequence step (the 'batch16' key)")
     ap.add_argument("--synthetic-context", action="store_true",
                     help="skip the prefill: set the context length directly (KV pages and recurrent state stay zero); for profiler runs")
     ap.add_argument("--no-spinup", action="store_true", help="skip the half second of untimed steps that brings the clocks up")
-    ap.add_argument("--exchange", default="peer", help="tensor-parallel exchange: 'peer' (own kernel over NVLink peer memory) or 'nccl'")
+    ap.add_argument("--exchange", default="peer", help="tensor-parallel exchange: 'peer' (own kernel over NVLink peer memory), 'peer-fused' (the same packets stored by "
+                    "the row-parallel matmul's epilogue and awaited by the next norm kernel; slower as measured) or 'nccl' (all-gather)")
     ap.add_argument("--model", default="dense27b", help="'dense27b' (the headline workload) or 'moe30b': the 30B-A3B-class "
                     "mixture-of-experts hybrid (group 32, 128 experts top-8 + shared) on a ragged batch of 32 sequences")
     ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit; "
-                    "'prefill': the same for the tcgen05 prefill-width matmul")
+                    "'prefill': the same for the tcgen05 prefill-width matmul; 'gdn': the gated-DeltaNet lane step alone on --seqs x --width rows; "
+                    "'attn': lane attention alone on --seqs x --width rows at --ctx")
     ap.add_argument("--shape", default="17408x5120")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=4, help="--only qmm: weight copies rotated through (4 x 50 MB > L2)")
@@ -332,7 +584,8 @@ def main():
         if rank != 0:
             return
         base = cpu_reference(args, rows)
-        print(json.dumps({"metric": "lane-verify rows/sec", "value": base["value"], "unit": "rows/s", "n_gpus": args.gpus,
+        gpu_leg = reference_gpu(args, rows)
+        print(json.dumps({"reference_gpu": gpu_leg, "metric": "lane-verify rows/sec", "value": base["value"], "unit": "rows/s", "n_gpus": args.gpus,
                           "steps": 1, "warmup": 0, "ms_per_step": 1000.0 * rows / base["value"], "higher_is_better": True,
                           "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
                           "config": config, "cpu_baseline": base,
@@ -358,9 +611,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         if args.model != "moe30b":
             try:
-                tp = distributed.RankGroup(exchange=args.exchange, hidden=synthetic.DENSE_27B["hidden"], device=dev)
+                tp = distributed.RankGroup(exchange="peer" if args.exchange == "peer-fused" else args.exchange,
+                                           hidden=synthetic.DENSE_27B["hidden"], device=dev, fused=args.exchange == "peer-fused")
             except Exception as exc:      # no symmetric memory between these GPUs: the library collective still works
-                if args.exchange != "peer":
+                if not args.exchange.startswith("peer"):
                     raise
                 print(f"bench: peer exchange unavailable ({type(exc).__name__}: {exc}); using the NCCL all-gather", file=sys.stderr)
                 args.exchange = "nccl"
@@ -371,6 +625,10 @@ def main():
 
     if args.only in ("qmm", "prefill"):
         return only_qmm(args, dev)
+    if args.only == "gdn":
+        return only_gdn(args, dev)
+    if args.only == "attn":
+        return only_attn(args, dev)
 
     if args.model == "moe30b":
         return bench_moe(args, dev, rank, world)
@@ -440,6 +698,33 @@ def main():
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_s = float(t.item())
 
+    # ---- extra: the same forward over 16 concurrent sequences x W rows (context set directly) ----
+    batch16 = None
+    if not args.no_batch16 and args.seqs == 1 and 16 * args.width <= 128:
+        st16 = F.State(w, 16, args.ctx + 2 * args.width, dev)
+        run16 = runner.LaneRunner(w, st16, [args.width] * 16, max_context=args.ctx + args.width, tp=tp)
+        run16.capture()
+        st16.lens = [args.ctx] * 16
+        run16.refresh()
+        run16.tokens.copy_(torch.randint(0, cfg.vocab, (16 * args.width,), generator=gen, device=dev, dtype=torch.int32))
+        for _ in range(3):
+            run16.step_device()
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(args.steps):
+            run16.step_device()
+        b1.record()
+        barrier()
+        ms16 = b0.elapsed_time(b1)
+        if world > 1:
+            t = torch.tensor([ms16], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms16 = float(t.item())
+        batch16 = {"seqs": 16, "rows": 16 * args.width, "ms_per_step": ms16 / args.steps,
+                   "rows_per_s": args.steps * 16 * args.width / (ms16 / 1000.0), "context": f"{args.ctx} (set directly: zero KV pages and state)"}
+        del run16, st16
+
     # ---- dominant kernel: the lane matmul, every launch of one forward replayed alone ----
     mats = []
     for layer in w.layers:
@@ -499,6 +784,9 @@ def main():
                     "frac_of_weight_roofline": (weight_bytes / (peak * 1e6)) / (ms / args.steps),
                     "qmm_ms_per_step": qmm_ms, "qmm_share": qmm_ms / (ms / args.steps)},
     }
+    if batch16 is not None:
+        batch16["frac_of_weight_roofline"] = (weight_bytes / (peak * 1e6)) / batch16["ms_per_step"]
+        line["batch16"] = batch16
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, rows)
     print(json.dumps(line), flush=True)

@@ -310,7 +310,10 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(const GdnFusedArgs a) {
         uint4 z_pre = make_uint4(0, 0, 0, 0), w_pre = make_uint4(0, 0, 0, 0);
         if (warp * 2 + (lane >> 4) < rows) {
             const int row = r0 + t0 + warp * 2 + (lane >> 4), l16 = lane & 15;
-            z_pre = *reinterpret_cast<const uint4*>(a.z + (size_t)row * a.z_stride + head * 128 + 8 * l16);
+            // two 8-byte loads: a row stride that is only a multiple of four values (narrow tensor-parallel shards)
+            const uint2* zp = reinterpret_cast<const uint2*>(a.z + (size_t)row * a.z_stride + head * 128 + 8 * l16);
+            const uint2 z0 = zp[0], z1 = zp[1];
+            z_pre = make_uint4(z0.x, z0.y, z1.x, z1.y);
             w_pre = reinterpret_cast<const uint4*>(a.norm_w)[l16];
         }
         __syncthreads();
@@ -416,9 +419,10 @@ int tf_gdn_fused(const void* qkv, size_t qkv_stride, const void* z, size_t z_str
     if (rows < 1 || rows > TF_QMM_MAX_ROWS || n_seqs < 1 || n_seqs > 65535 || k_heads < 1 || v_heads < 1 || v_heads % k_heads) return TF_EINVAL;
     if (dk != 128 || dv != 128 || taps != 4 || (group != 64 && group != 32)) return TF_EINVAL;
     if (!qkv || !z || !a || !b || !conv_state || !conv_w || !a_log || !dt_bias || !norm_w || !state || !seq_start) return TF_EINVAL;
-    if (!k_out || !v_out || !g_out || !beta_out || (!out_packed && !out_rows) || qkv_stride % 4 || z_stride % 8) return TF_EINVAL;
+    if (!k_out || !v_out || !g_out || !beta_out || (!out_packed && !out_rows) || qkv_stride % 4 || z_stride % 4) return TF_EINVAL;
     if (((uintptr_t)qkv | (uintptr_t)conv_state | (uintptr_t)k_out | (uintptr_t)v_out) & 7) return TF_EALIGN;
-    if (((uintptr_t)conv_w | (uintptr_t)z | (uintptr_t)norm_w | (uintptr_t)state | (uintptr_t)out_packed | (uintptr_t)out_rows) & 15) return TF_EALIGN;
+    if (((uintptr_t)z) & 7) return TF_EALIGN;
+    if (((uintptr_t)conv_w | (uintptr_t)norm_w | (uintptr_t)state | (uintptr_t)out_packed | (uintptr_t)out_rows) & 15) return TF_EALIGN;
     tf::GdnFusedArgs g = {};
     g.qkv = static_cast<const __nv_bfloat16*>(qkv); g.qkv_stride = qkv_stride;
     g.z = static_cast<const __nv_bfloat16*>(z); g.z_stride = z_stride;

@@ -59,7 +59,8 @@ class RankGroup:
     kernel. ``exchange="nccl"``: ``all_gather_into_tensor`` on the current stream (gloo on CPU in
     tests). Never an all-reduce: the sum is done in rank order by the consuming kernel."""
 
-    def __init__(self, group=None, exchange: str = "nccl", max_rows: int = 128, hidden: int = 0, device=None):
+    def __init__(self, group=None, exchange: str = "nccl", max_rows: int = 128, hidden: int = 0, device=None,
+                 fused: bool = False):
         import torch.distributed as dist
 
         self.dist = dist
@@ -68,6 +69,7 @@ class RankGroup:
         self.rank = dist.get_rank(group)
         self.exchange = exchange
         self.count = 0                      # exchanges issued so far (slots alternate)
+        self.fuse = bool(fused)
         if exchange == "peer":
             import os
 
@@ -115,7 +117,7 @@ class RankGroup:
         """Whether the exchange rides inside the row-parallel matmul's epilogue and the next norm kernel
         (``tf_qmm_peer`` / ``tf_norm_xs_peer``) instead of being a step of its own."""
 
-        return self.exchange == "peer"
+        return self.exchange == "peer" and self.fuse
 
     def peer_args(self):
         """(buffer pointer table, slot bytes, exchange-number word, ticket word, this rank's buffer) for the fused form."""

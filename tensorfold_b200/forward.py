@@ -113,6 +113,11 @@ def _stack(parts, device, group) -> QWeight:
     words = torch.cat([p.words for p in parts]).to(device)
     scales = torch.cat([p.scales for p in parts]).to(device)
     biases = torch.cat([p.biases for p in parts]).to(device)
+    pad = -words.shape[0] % 8
+    if pad:      # output rows in whole 16-byte units (narrow tensor-parallel shards): zero projections, never read
+        words = torch.cat([words, words.new_zeros((pad, words.shape[1]))])
+        scales = torch.cat([scales, scales.new_zeros((pad, scales.shape[1]))])
+        biases = torch.cat([biases, biases.new_zeros((pad, biases.shape[1]))])
     return tile_weight(words.contiguous(), scales.contiguous(), biases.contiguous(), group)
 
 
@@ -301,7 +306,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     rec = Record(b, torch.empty((ng, R, c.k_heads, c.dk), **bf), torch.empty((ng, R, c.v_heads, c.dv), **bf),
                  torch.empty((ng, R, c.v_heads), dtype=torch.float32, device=dev),
                  torch.empty((ng, R, c.v_heads), dtype=torch.float32, device=dev),
-                 torch.empty((ng, R, 2 * kd + 2 * vd + 2 * c.v_heads), **bf),
+                 torch.empty((ng, R, -(-(2 * kd + 2 * vd + 2 * c.v_heads) // 8) * 8), **bf),
                  torch.empty((na, R, c.kv_heads, c.head_dim), **bf), torch.empty((na, R, c.kv_heads, c.head_dim), **bf))
     q_att = torch.empty((R, c.heads, c.head_dim), **bf)
     att_in = torch.empty((R, c.heads * 2 * c.head_dim + 2 * c.kv_heads * c.head_dim), **bf)
@@ -342,7 +347,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
         if layer.linear:
             proj = lane_matmul(h, layer.in_proj, out=rec.gdn_in[gi], next_weight=layer.out_proj)
             qkv, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
-            bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + c.v_heads], proj[:, 2 * kd + 2 * vd + c.v_heads:]
+            bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + c.v_heads], proj[:, 2 * kd + 2 * vd + c.v_heads:2 * kd + 2 * vd + 2 * c.v_heads]
             # conv + gates, recurrence and gated norm in one launch; k, v, g, beta land in the record for the commit
             mixed = lane_gdn.gdn_mixer(qkv, z, aa, bb, st.conv[gi], layer.conv, layer.A_log, layer.dt_bias, layer.norm, st.rec[gi],
                                        b.seq_start, nk=c.k_heads, nv=c.v_heads, eps=c.eps, group=g,

@@ -64,7 +64,7 @@ def random_weights(cfg: Config, seed: int = 0, device="cuda", rank: int = 0, wor
             gate_up = random_q4(gen, 2 * sc.intermediate, cfg.hidden, g, device)
             down = random_q4(gen, cfg.hidden, sc.intermediate, g, device)
         if linear:
-            lw = LayerWeights(True, inorm, pnorm, random_q4(gen, 2 * kd + 2 * vd + 2 * sc.v_heads, cfg.hidden, g, device),
+            lw = LayerWeights(True, inorm, pnorm, random_q4(gen, -(-(2 * kd + 2 * vd + 2 * sc.v_heads) // 8) * 8, cfg.hidden, g, device),
                               random_q4(gen, cfg.hidden, vd, g, device), gate_up, down,
                               conv=(0.3 * torch.randn((2 * kd + vd, 4), generator=gen, device=device)).to(bf),
                               A_log=0.5 * torch.randn(sc.v_heads, generator=gen, device=device),

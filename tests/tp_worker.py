@@ -79,11 +79,13 @@ def main():
     # the exchange fused into the matmul epilogue and the norm kernel carries the bits of the plain
     # all-gather + rank-ordered sum (same order, one rounding)
     fused_ok = True
-    if tp.fused:
-        tp2 = distributed.RankGroup(exchange="nccl")
+    if tp.exchange == "peer":
         st3 = F.State(w, 1, 256, dev)
-        l1n, _ = F.tree_forward(w, torch.tensor(tokens[:12], dtype=torch.int32, device=dev), [-1] + list(range(11)), st3, tp=tp2)
-        fused_ok = bool(torch.equal(l1n.view(torch.int16), l1.view(torch.int16)))
+        tp_fused = distributed.RankGroup(exchange="peer", hidden=cfg.hidden, device=dev, fused=True)
+        tp_nccl = distributed.RankGroup(exchange="nccl")
+        for other in (tp_fused, tp_nccl):
+            l1n, _ = F.tree_forward(w, torch.tensor(tokens[:12], dtype=torch.int32, device=dev), [-1] + list(range(11)), st3, tp=other)
+            fused_ok &= bool(torch.equal(l1n.view(torch.int16), l1.view(torch.int16)))
     flags = torch.tensor([int(same), int(head_ok), int(fused_ok)], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
