@@ -701,7 +701,8 @@ def main():
     # ---- extra: the same forward over 16 concurrent sequences x W rows (context set directly) ----
     batch16 = None
     if not args.no_batch16 and args.seqs == 1 and 16 * args.width <= 128:
-        st16 = F.State(w, 16, args.ctx + 2 * args.width, dev)
+        F.enable_wide(w)                 # 128 rows a step: the tcgen05 wide-row kernel for every matmul of this state
+        st16 = F.State(w, 16, args.ctx + 2 * args.width, dev, wide=True)
         run16 = runner.LaneRunner(w, st16, [args.width] * 16, max_context=args.ctx + args.width, tp=tp)
         run16.capture()
         st16.lens = [args.ctx] * 16
@@ -721,7 +722,7 @@ def main():
             t = torch.tensor([ms16], device=dev)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             ms16 = float(t.item())
-        batch16 = {"seqs": 16, "rows": 16 * args.width, "ms_per_step": ms16 / args.steps,
+        batch16 = {"seqs": 16, "rows": 16 * args.width, "ms_per_step": ms16 / args.steps, "matmul": "tcgen05 wide-row kernel (bf16 x bf16 -> fp32 in tensor memory)",
                    "rows_per_s": args.steps * 16 * args.width / (ms16 / 1000.0), "context": f"{args.ctx} (set directly: zero KV pages and state)"}
         del run16, st16
 

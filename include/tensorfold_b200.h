@@ -115,26 +115,32 @@ int tf_qmm_untile(const void* w_tiled, void* words, void* scales, void* biases, 
                   void* stream);
 
 
-/* ---- prefill-width 4-bit matmul on tcgen05 tensor cores ---------------------------------------
- * Replaces: the dense bf16 GEMM the reference's prompt prefill runs after dequantising a layer
- * (families/qwen3_5/cuda/forward.py prefill path; runtime/serve.py prompt admission) — a PHASE of a
- * request, chosen by the caller, never by the row count of a verify window.
+/* ---- wide-row 4-bit matmul on tcgen05 tensor cores -------------------------------------------
+ * No counterpart in the reference: its prompt prefill and its many-row verify windows go through the
+ * same lane kernels in chains of up to 128 rows (families/qwen3_5/cuda/decode.py:34-60,
+ * qmm_fast.py:108-140). This kernel is this library's own wide-row path: 32..128 rows per launch on
+ * tcgen05.mma with the accumulators in tensor memory.
  *
- * Same formula as tf_qmm, different arithmetic, hence different bits: each activation is carried as
- * two e4m3 planes hi + lo of x * 2^E (E a power of two per row and group that brings the group's
- * largest magnitude into [128, 256)), the 4-bit weight codes are the e4m3 values q * 2^-9, and the
- * products are summed by tcgen05.mma kind::f8f6f4 into fp32 accumulators in tensor memory. Results
- * are within the bf16 bound of tf_qmm's (|x| below 2^-8 of its group's largest lose precision) and
- * are independent of the number of rows in the call within this kernel; a request's serial decode
- * and verify windows must not mix it with tf_qmm.
+ * Same formula as tf_qmm, different arithmetic, hence different bits: the 4-bit codes are dequantised
+ * to bf16 weights bf16(s * q + b) (one fused multiply-add, one rounding) and multiplied with the bf16
+ * activations by tcgen05.mma kind::f16 into fp32 accumulators (M = 128 output columns, N = the row
+ * bucket 32/64/128, K = 16); K segments are added in k order and rounded once. Results are within the
+ * bf16 bound of tf_qmm's and do not depend on the number of rows in the call; an engine must run all
+ * its steps (serial and windowed) through one of the two kernels, never a mixture.
  *
- * x_packed: tf_packed_tc_bytes bytes from tf_pack_rows_tc; w_tiled: tf_qmm_tc_tiled_bytes bytes from
- * tf_qmm_tc_tile (a different order from tf_qmm_tile's). scratch as for tf_qmm. M is 1..128. */
+ * x_packed: tf_packed_tc_bytes bytes from tf_pack_rows_tc (row-major bf16 rows; xs is ignored and may
+ * be NULL) or from tf_repack_tc (the lane kernel's packed rows, as every glue kernel writes them);
+ * w_tiled: tf_qmm_tc_tiled_bytes bytes from tf_qmm_tc_tile (a different order from tf_qmm_tile's).
+ * scratch as for tf_qmm. M is 1..128 per launch. */
 size_t tf_packed_tc_bytes(int M, int K, int group);
 size_t tf_qmm_tc_tiled_bytes(int N, int K, int group);
 int tf_qmm_tc(const void* x_packed, const void* w_tiled, void* y, void* scratch, size_t scratch_bytes, int M, int N,
               int K, int group, int flags, int* status, void* stream);
 int tf_pack_rows_tc(const void* x, void* x_packed, void* xs, int M, int K, int group, void* stream);
+int tf_repack_tc(const void* lane_packed, void* x_packed, int M, int K, int group, void* stream);
+/* Profiling hook (no reference counterpart): with a device buffer of 148 * 16 64-bit words set, the latest
+ * tf_qmm_tc launch writes 16 globaltimer stamps (ns) per worker (roles' milestones); NULL switches it off. */
+int tf_qmm_tc_set_trace(void* stamps);
 int tf_qmm_tc_tile(const void* words, const void* scales, const void* biases, void* w_tiled, int N, int K, int group,
                    void* stream);
 int tf_qmm_tc_untile(const void* w_tiled, void* words, void* scales, void* biases, int N, int K, int group,

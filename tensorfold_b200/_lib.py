@@ -42,6 +42,8 @@ SIGNATURES: dict[str, tuple] = {
     "tf_qmm_tc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                           c_void_p, c_void_p]),
     "tf_pack_rows_tc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tf_qmm_tc_set_trace": (c_int, [c_void_p]),
+    "tf_repack_tc": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_tc_tile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_tc_untile": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_norm_xs": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -107,7 +109,7 @@ SIGNATURES: dict[str, tuple] = {
 
 _lib = None
 _launches = 0          # kernel-launching entry points called so far (what a CUDA graph of a step holds)
-_NO_LAUNCH = {"tf_version", "tf_qmm_set_trace", "tf_set_poll_limit", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
+_NO_LAUNCH = {"tf_version", "tf_qmm_set_trace", "tf_qmm_tc_set_trace", "tf_set_poll_limit", "tf_qmm_workers", "tf_qmm_scratch_bytes", "tf_packed_bytes", "tf_qmm_tiled_bytes",
               "tf_attention_scratch_bytes", "tf_attention_chunks", "tf_packed_tc_bytes", "tf_qmm_tc_tiled_bytes", "tf_topk_scratch_bytes", "tf_moe_max_problems", "tf_moe_slot_bytes", "tf_peer_slot_bytes"}
 
 

@@ -20,7 +20,8 @@ import torch
 from . import lane_attention as LA
 from . import lane_gdn, lane_glue
 from . import lane_moe
-from .lane_qmm import MAX_ROWS, QWeight, lane_matmul, new_packed, tile_weight
+from .lane_qmm import MAX_ROWS, QWeight, new_packed, tile_weight
+from .lane_qmm import lane_matmul as _lane_matmul
 
 
 @dataclass
@@ -94,6 +95,7 @@ class Weights:
     norm: torch.Tensor
     head: QWeight
     inv_freq: torch.Tensor
+    wide: dict | None = None          # id(QWeight) -> prefill_qmm.TCWeight, made by enable_wide
 
     def nbytes(self) -> int:
         """Bytes of 4-bit projection weights one forward streams (the weight-bytes roofline numerator)."""
@@ -104,6 +106,26 @@ class Weights:
             if l.experts is None:
                 total += l.gate_up.nbytes() + l.down.nbytes()
         return total
+
+
+def enable_wide(w: Weights) -> Weights:
+    """Give every dense projection of ``w`` a twin in the wide-row kernel's tile layout (``prefill_qmm``), so that
+    a ``State`` made with ``wide=True`` runs all its steps - serial and windowed - on the tcgen05 kernel (many
+    concurrent sequences: 32..128 rows a step). Doubles the weight memory; the lane tiles stay for states made
+    without it. A row's bits are then the wide kernel's in every step of that state."""
+
+    from . import prefill_qmm
+    from .lane_qmm import untile_weight
+
+    if w.wide is None:
+        w.wide = {}
+        mats = [w.head]
+        for l in w.layers:
+            mats += [l.in_proj, l.out_proj] + ([l.gate_up, l.down] if l.experts is None else [])
+        for q in mats:
+            words, scales, biases = untile_weight(q)
+            w.wide[id(q)] = prefill_qmm.tile_weight(words, scales, biases, q.group)
+    return w
 
 
 def _stack(parts, device, group) -> QWeight:
@@ -160,9 +182,13 @@ class State:
     recurrent state for the GDN layers, and each sequence's committed length. Read-only during a
     forward; only ``commit`` writes it (reference: ``forward.State``)."""
 
-    def __init__(self, w: Weights, n_seqs: int, max_context: int, device=None, num_pages: int | None = None):
+    def __init__(self, w: Weights, n_seqs: int, max_context: int, device=None, num_pages: int | None = None,
+                 wide: bool = False):
         c = w.config
         device = device or w.norm.device
+        if wide and w.wide is None:
+            raise ValueError("State(wide=True) needs weights prepared by enable_wide")
+        self.wide = bool(wide)        # every step of this state multiplies on the wide-row (tcgen05) kernel
         self.n_seqs = n_seqs
         self.lens = [0] * n_seqs
         self.seq_lens = torch.zeros(n_seqs, dtype=torch.int32, device=device)
@@ -319,7 +345,19 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
     scratch = torch.empty(LA.scratch_bytes(R, c.heads, c.head_dim, b.max_chunks), dtype=torch.uint8, device=dev)
     scale = c.head_dim ** -0.5
 
-    fused_tp = tp is not None and getattr(tp, "fused", False)
+    fused_tp = tp is not None and getattr(tp, "fused", False) and not st.wide
+    if st.wide:
+        from . import prefill_qmm
+
+        if c.experts:
+            raise ValueError("tree_forward: the wide-row kernel covers the dense projections only")
+        kmax = max(q.k for q in (w.head, *(m for l in w.layers for m in (l.in_proj, l.out_proj, l.gate_up, l.down))))
+        staging = torch.empty(prefill_qmm.packed_bytes(R, kmax, g), dtype=torch.uint8, device=dev)
+
+        def lane_matmul(x_, weight, *, f32=False, out=None, next_weight=None, peer=None):      # noqa: F811
+            return prefill_qmm.prefill_matmul(x_, w.wide[id(weight)], f32=f32, out=out, staging=staging)
+    else:
+        lane_matmul = _lane_matmul
 
     def row_parallel(act, weight, nxt):
         """(residual rows, gathered partials): one of the two is None; both are when the exchange is fused

@@ -1,11 +1,11 @@
-"""Prefill-width 4-bit projections on the tcgen05 tensor cores.
+"""Wide-row 4-bit projections on the tcgen05 tensor cores.
 
-Prompt prefill is a phase of a request with its own arithmetic (the reference dequantises a layer
-and calls a dense GEMM there: ``families/qwen3_5/cuda/forward.py`` prefill path); exact row-in-window
-equality is a property of the verify regime, which always runs ``lane_qmm.lane_matmul``. This module
-is the wide-row counterpart: the same 4-bit weights, regrouped for ``csrc/qmm_tc.cu``, multiplied on
-``tcgen05.mma`` with activations split into two e4m3 planes. A row's bits are still independent of the
-other rows in the call, but they are this kernel's bits, not the lane kernel's.
+The reference runs prompt prefill and many-row windows through its lane kernels in chains of up to 128
+rows (``families/qwen3_5/cuda/decode.py:34-60``); this module is this library's own wide-row path:
+the same 4-bit weights, regrouped for ``csrc/qmm_tc.cu``, dequantised to bf16 in flight and multiplied on
+``tcgen05.mma`` (bf16 x bf16 -> fp32 in tensor memory). A row's bits are independent of the other rows
+in the call, but they are this kernel's bits, not the lane kernel's: an engine runs all its steps through
+one of the two.
 """
 
 from __future__ import annotations
@@ -54,34 +54,60 @@ def untile_weight(q: TCWeight) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor
     return words, scales, biases
 
 
-def prefill_matmul(x: torch.Tensor, weight: TCWeight, *, f32: bool = False) -> torch.Tensor:
-    """x (..., K) bf16 times the 4-bit ``weight`` (N, K) transposed -> (..., N), in launches of up to
-    ``MAX_ROWS`` rows."""
+def packed_bytes(rows: int, k: int, group: int) -> int:
+    return int(_lib.load().tf_packed_tc_bytes(rows, k, group))
 
-    if x.dtype != torch.bfloat16:
-        raise ValueError("prefill_matmul: x must be bf16")
-    if x.shape[-1] != weight.k:
-        raise ValueError(f"prefill_matmul: weight (N={weight.n}, K={weight.k}) does not match K={x.shape[-1]}")
-    _lib.need_cuda(x)
+
+def prefill_matmul(x, weight: TCWeight, *, f32: bool = False, out: torch.Tensor | None = None,
+                   staging: torch.Tensor | None = None) -> torch.Tensor:
+    """x (..., K) bf16 (or a ``lane_qmm.Packed``: the rows every glue kernel writes, at most ``MAX_ROWS``)
+    times the 4-bit ``weight`` (N, K) transposed -> (..., N), in launches of up to ``MAX_ROWS`` rows.
+    ``staging``: a uint8 buffer of ``packed_bytes(rows, K, group)`` for the regrouped rows (so that a
+    captured step allocates nothing)."""
+
+    from .lane_qmm import Packed
+
     lib = _lib.load()
-    lead, dev = x.shape[:-1], x.device
-    x2 = x.reshape(-1, weight.k).contiguous()
-    m = x2.shape[0]
+    if isinstance(x, Packed):
+        if x.k != weight.k or x.group != weight.group:
+            raise ValueError("prefill_matmul: packed rows do not match the weight")
+        dev, m, lead = x.data.device, x.m, (x.m,)
+        x2 = None
+    else:
+        if x.dtype != torch.bfloat16:
+            raise ValueError("prefill_matmul: x must be bf16")
+        if x.shape[-1] != weight.k:
+            raise ValueError(f"prefill_matmul: weight (N={weight.n}, K={weight.k}) does not match K={x.shape[-1]}")
+        _lib.need_cuda(x)
+        lead, dev = x.shape[:-1], x.device
+        x2 = x.reshape(-1, weight.k).contiguous()
+        m = x2.shape[0]
     if m < 1:
         raise ValueError("prefill_matmul: needs at least one row")
-    out = torch.empty((m, weight.n), dtype=torch.float32 if f32 else torch.bfloat16, device=dev)
+    dtype = torch.float32 if f32 else torch.bfloat16
+    if out is None:
+        out = torch.empty((m, weight.n), dtype=dtype, device=dev)
+    elif out.shape != (m, weight.n) or out.dtype != dtype or not out.is_contiguous():
+        raise ValueError("prefill_matmul: out has the wrong shape or dtype")
     scratch = scratch_for(dev)
     st = _lib.status(dev)
     with torch.cuda.device(dev):
         for r0 in range(0, m, MAX_ROWS):
             rows = min(MAX_ROWS, m - r0)
-            packed = torch.empty(lib.tf_packed_tc_bytes(rows, weight.k, weight.group), dtype=torch.uint8, device=dev)
-            _lib.check(lib.tf_pack_rows_tc(x2[r0:r0 + rows].data_ptr(), packed.data_ptr(), None, rows, weight.k,
-                                           weight.group, _lib.stream()), "prefill pack_rows")
+            need = lib.tf_packed_tc_bytes(rows, weight.k, weight.group)
+            packed = staging if staging is not None else torch.empty(need, dtype=torch.uint8, device=dev)
+            if packed.numel() < need:
+                raise ValueError("prefill_matmul: staging buffer too small")
+            if x2 is None:
+                _lib.check(lib.tf_repack_tc(x.data.data_ptr(), packed.data_ptr(), rows, weight.k, weight.group, _lib.stream()),
+                           "prefill repack")
+            else:
+                _lib.check(lib.tf_pack_rows_tc(x2[r0:r0 + rows].data_ptr(), packed.data_ptr(), None, rows, weight.k,
+                                               weight.group, _lib.stream()), "prefill pack_rows")
             _lib.check(lib.tf_qmm_tc(packed.data_ptr(), weight.tiled.data_ptr(), out[r0:r0 + rows].data_ptr(),
                                      scratch.data_ptr(), scratch.numel(), rows, weight.n, weight.k, weight.group,
                                      1 if f32 else 0, st.word.data_ptr(), _lib.stream()), "prefill_matmul")
     return out.reshape(*lead, weight.n)
 
 
-__all__ = ["TCWeight", "prefill_matmul", "tile_weight", "untile_weight"]
+__all__ = ["TCWeight", "packed_bytes", "prefill_matmul", "tile_weight", "untile_weight"]
