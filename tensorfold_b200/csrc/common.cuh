@@ -115,6 +115,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     report(status, TF_ESTALL);
     return false;
 }
+// The same for a role that waits long and must not take issue slots from the warps that work meanwhile: each
+// poll lets the hardware suspend the thread for up to `ns` nanoseconds (or until the phase completes).
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, int* status, uint32_t ns = 2000, int limit = 1 << 20) {
+    for (int i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(ns)
+            : "memory");
+        if (ok) return true;
+    }
+    report(status, TF_ESTALL);
+    return false;
+}
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier. Both addresses
 // 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

@@ -66,37 +66,42 @@ constexpr int kItemTiles = 4;   // k tiles per schedule item: the same for every
                                 // K segments (hence the bits) do not depend on the row count
 constexpr int kCols = 128;      // columns per column block = TMEM lanes = tensor-core M
 constexpr int kDequant = 16;         // dequantiser warps: four per TMEM lane quarter, one k-step (16 inputs) of a k tile each
-constexpr int kThreads = (kDequant + 6) * 32;   // dequantisers, producer, MMA issuer, 4 epilogue
+constexpr int kThreads = (kDequant + 7) * 32;   // dequantisers, weight producer, MMA issuer, 4 epilogue, activation producer
 
 __host__ __device__ constexpr int rec_bytes(int group) { return 4096 + 512 * (64 / group); }
 __host__ __device__ constexpr int pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
-// A pipeline stage is KTS k tiles of one column block: their weight records and the activation tiles. The A
-// operand ring holds AU stages of dequantised tiles (32 tensor-memory columns a tile: 64 inputs as bf16 pairs),
-// the accumulator ring DU column-block accumulators of NB columns.
-template <int G, int NB, int KTS, int STAGES>
+// A pipeline stage is KTS k tiles of one column block. Their weight records and their activation tiles travel in
+// two rings of their own: the small weight ring (WS stages) lets the dequantisers run ahead of the tensor core,
+// the activation ring (XS stages of KTS * NB * 128 bytes) only has to cover the copy behind the running products.
+// The A operand ring holds AU stages of dequantised tiles (32 tensor-memory columns a tile: 64 inputs as bf16
+// pairs), the accumulator ring DU column-block accumulators of NB columns.
+template <int G, int NB, int KTS, int XS>
 struct Cfg {
     static constexpr int REC = rec_bytes(G);
     static constexpr int GPT = 64 / G;                     // groups per k tile
     static constexpr int XTILE = NB * 128;                 // packed activation bytes per k tile
-    static constexpr int W_BYTES = KTS * REC;
-    static constexpr int X_BYTES = KTS * XTILE;            // activation tiles first: swizzle atoms want 1024-byte alignment
-    static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + 1023) / 1024) * 1024;
+    static constexpr int W_BYTES = ((KTS * REC + 127) / 128) * 128;
+    static constexpr int X_BYTES = KTS * XTILE;            // swizzle atoms want 1024-byte alignment: activations first
+    static constexpr int WS = 4;
     static constexpr int DU = 2;
     static constexpr int AU_FIT = (512 - DU * NB) / (KTS * 32);
-    static constexpr int AU = AU_FIT > 4 ? 4 : AU_FIT;   // as deep as tensor memory allows: the ring hides the tensor core's completion latency
-    static constexpr int NBARS = 2 * STAGES + 2 * AU + 2 * DU;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + NBARS * 8 + 128 + 1024;
+    static constexpr int AU = AU_FIT > 4 ? 4 : AU_FIT;   // as deep as tensor memory allows
+    static constexpr int NBARS = 2 * XS + 2 * WS + 2 * AU + 2 * DU;
+    static constexpr int SMEM = XS * X_BYTES + WS * W_BYTES + NBARS * 8 + 128 + 1024;
     static constexpr int A_COLS = AU * KTS * 32;
     static constexpr int D_COL0 = A_COLS;
     static constexpr int TMEM_COLS = pow2_cols(A_COLS + DU * NB);
     static_assert(A_COLS + DU * NB <= 512, "rings do not fit tensor memory");
+    static_assert(AU >= 2, "the dequantisers need a slot to run ahead into");
 };
 
-// Optional per-CTA timeline for profiling (tf_qmm_tc_set_trace): the latest launch writes 16 globaltimer stamps (ns) per CTA:
-// 0 entry, 1 tensor memory allocated, 2 producer past griddepcontrol.wait, 3 dequantisers past their first full
-// barrier, 4 first stage dequantised, 5 first tensor-core step issued, 6 last stage dequantised, 7 last step issued,
-// 8 epilogue past its first accumulator barrier, 9 epilogue done, 10 exit, 11 producer's last copy issued.
+// Optional per-CTA timeline for profiling (tf_qmm_tc_set_trace): the latest launch writes 16 globaltimer stamps (ns)
+// per CTA: 0 entry, 1 tensor memory allocated, 2 activation producer past griddepcontrol.wait, 3 dequantisers past
+// their first full barrier, 4 first stage dequantised, 5 first tensor-core step issued, 6 last stage dequantised,
+// 7 last step issued, 8 epilogue past its first accumulator barrier, 9 epilogue done, 10 past the closing barrier
+// (the stamp may be read early by the compiler), 11 weight producer's last copy issued, 12/13 first stage's
+// tensor-memory stores issued / complete, 14 first accumulator batch loaded, 15 first segment stored.
 __device__ long long* g_tc_trace = nullptr;
 __device__ __forceinline__ void tc_stamp(long long* tr, int slot) {
     if (tr != nullptr) {
@@ -135,6 +140,11 @@ __host__ __device__ inline int worker_begin(int cta, int CB, int SPB) {
 constexpr size_t kSlotFloats = (size_t)TF_QMM_MAX_ROWS * kCols;
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -283,16 +293,15 @@ struct StageWalk {
     }
 };
 
-template <int G, int NB, int KTS, int STAGES>
+template <int G, int NB, int KTS, int XS>
 __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant__ Args a) {
-    using C = Cfg<G, NB, KTS, STAGES>;
+    using C = Cfg<G, NB, KTS, XS>;
+    constexpr int WS = C::WS;
     static_assert(kItemTiles % KTS == 0, "a schedule item is a whole number of pipeline stages");
     constexpr int AU = C::AU, DU = C::DU;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int seg_list[kWorkers + 2];
     __shared__ uint32_t tmem_base_s;
-    __shared__ volatile int epi_finished;
-    if (threadIdx.x == 0) epi_finished = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long* tr = g_tc_trace;
     if (threadIdx.x == 0) tc_stamp(tr, 0);
@@ -303,18 +312,22 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
     const int begin = worker_begin(blockIdx.x, CB, SPB), end = worker_begin(blockIdx.x + 1, CB, SPB);
     if (begin >= end) return;                             // a worker without work (whole CTA leaves together)
 
-    uint8_t* stage0 = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
-    const uint32_t bars = smem_u32(stage0 + STAGES * C::STAGE_BYTES);
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto a_full = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-    auto a_empty = [&](int s) { return bars + 8u * (2 * STAGES + AU + s); };
-    auto d_full = [&](int s) { return bars + 8u * (2 * STAGES + 2 * AU + s); };
-    auto d_empty = [&](int s) { return bars + 8u * (2 * STAGES + 2 * AU + DU + s); };
+    uint8_t* xring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+    uint8_t* wring = xring + XS * C::X_BYTES;
+    const uint32_t bars = smem_u32(wring + WS * C::W_BYTES);
+    auto x_full = [&](int s) { return bars + 8u * s; };
+    auto x_empty = [&](int s) { return bars + 8u * (XS + s); };
+    auto w_full = [&](int s) { return bars + 8u * (2 * XS + s); };
+    auto w_empty = [&](int s) { return bars + 8u * (2 * XS + WS + s); };
+    auto a_full = [&](int s) { return bars + 8u * (2 * XS + 2 * WS + s); };
+    auto a_empty = [&](int s) { return bars + 8u * (2 * XS + 2 * WS + AU + s); };
+    auto d_full = [&](int s) { return bars + 8u * (2 * XS + 2 * WS + 2 * AU + s); };
+    auto d_empty = [&](int s) { return bars + 8u * (2 * XS + 2 * WS + 2 * AU + DU + s); };
 
     if (threadIdx.x == 0) {
-        // a stage is free when the dequantiser warps have read its weights and the tensor core its activations
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), kDequant + 1); }
+        // a weight stage is free when the dequantiser warps have read it, an activation stage when the tensor core has
+        for (int s = 0; s < XS; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
+        for (int s = 0; s < WS; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), kDequant); }
         for (int s = 0; s < AU; ++s) { mbar_init(a_full(s), kDequant); mbar_init(a_empty(s), 1); }
         for (int s = 0; s < DU; ++s) { mbar_init(d_full(s), 1); mbar_init(d_empty(s), 4); }
         mbar_fence_init();
@@ -334,52 +347,46 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
     // the first and the last segment of this CTA's range may be parts of a column block
 
     if (warp == kDequant) {
-        // ------------------------------- producer: one thread ----------------------------------
-        // Weights never change during a forward, so the first ring of weight copies is issued before
-        // waiting for the previous kernel; the activations (its output) follow after the wait.
+        // ------------------------------- weight producer: one thread ----------------------------------
+        // Weights never change during a forward: their copies do not wait for the previous kernel.
         if (lane == 0) {
-            Ring ring(STAGES, 1);
-            int issued = 0;
-            int early_kt0[STAGES], early_nkt[STAGES];
-            bool waited = false;
+            Ring ring(WS, 1);
             for (StageWalk<KTS> wk(begin, end, SPB, KT); wk.valid(); wk.advance()) {
-                const int kt0 = wk.kt0(), nkt = wk.nkt();
-                if (issued == STAGES && !waited) {
-                    pdl_wait();
-                    tc_stamp(tr, 2);
-                    for (int e = 0; e < STAGES; ++e)
-                        bulk_g2s(smem_u32(stage0 + e * C::STAGE_BYTES), a.xp + (size_t)early_kt0[e] * C::XTILE,
-                                 (uint32_t)(early_nkt[e] * C::XTILE), full_bar(e));
-                    waited = true;
-                }
-                mbar_wait(empty_bar(ring.i), ring.phase, a.status);
-                uint8_t* sb = stage0 + ring.i * C::STAGE_BYTES;
-                const uint32_t wbytes = (uint32_t)(nkt * C::REC), xbytes = (uint32_t)(nkt * C::XTILE);
-                mbar_arrive_expect_tx(full_bar(ring.i), wbytes + xbytes);
-                bulk_g2s(smem_u32(sb + C::X_BYTES), a.w + ((size_t)wk.cb * KT + kt0) * C::REC, wbytes, full_bar(ring.i));
-                if (waited) bulk_g2s(smem_u32(sb), a.xp + (size_t)kt0 * C::XTILE, xbytes, full_bar(ring.i));
-                else { early_kt0[issued] = kt0; early_nkt[issued] = nkt; }
-                ++issued;
+                const uint32_t wbytes = (uint32_t)(wk.nkt() * C::REC);
+                mbar_wait_idle(w_empty(ring.i), ring.phase, a.status, 500);
+                mbar_arrive_expect_tx(w_full(ring.i), wbytes);
+                bulk_g2s(smem_u32(wring + ring.i * C::W_BYTES), a.w + ((size_t)wk.cb * KT + wk.kt0()) * C::REC, wbytes, w_full(ring.i));
                 ring.next();
             }
             tc_stamp(tr, 11);
-            if (!waited) {
-                pdl_wait();
-                tc_stamp(tr, 2);
-                for (int e = 0; e < issued; ++e)
-                    bulk_g2s(smem_u32(stage0 + e * C::STAGE_BYTES), a.xp + (size_t)early_kt0[e] * C::XTILE,
-                             (uint32_t)(early_nkt[e] * C::XTILE), full_bar(e));
-            }
         }
         __syncwarp();            // the warp reaches the closing barrier together
-    } else if (warp == kDequant + 1) {
-        // ------------------------------- MMA issuer: one thread ---------------------------------
+    } else if (warp == kDequant + 6) {
+        // ------------------------------- activation producer: one thread ------------------------------
         if (lane == 0) {
+            pdl_wait();          // the activations are the previous kernel's output
+            tc_stamp(tr, 2);
+            Ring ring(XS, 1);
+            for (StageWalk<KTS> wk(begin, end, SPB, KT); wk.valid(); wk.advance()) {
+                const uint32_t xbytes = (uint32_t)(wk.nkt() * C::XTILE);
+                mbar_wait_idle(x_empty(ring.i), ring.phase, a.status, 500);
+                mbar_arrive_expect_tx(x_full(ring.i), xbytes);
+                bulk_g2s(smem_u32(xring + ring.i * C::X_BYTES), a.xp + (size_t)wk.kt0() * C::XTILE, xbytes, x_full(ring.i));
+                ring.next();
+            }
+        }
+        __syncwarp();
+    } else if (warp == kDequant + 1) {
+        // ------------------------------- MMA issuer ------------------------------------------------
+        // The whole warp walks the stages converged (so that addresses and descriptors live in uniform registers);
+        // one elected lane issues the tensor-core instructions.
+        {
             // fp32 D, bf16 x bf16, A from tensor memory, B K-major from shared memory, N = row bucket, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(kCols >> 4) << 24);
-            Ring stage(STAGES, 0), ar(AU, 0), dr(DU, 1);
+            Ring xr(XS, 0), ar(AU, 0), dr(DU, 1);
             int cur_cb = -1;
             uint32_t accumulate = 0;
+            const bool leader = elect_one();
             for (StageWalk<KTS> wk(begin, end, SPB, KT); wk.valid();) {
                 const int nkt = wk.nkt();
                 if (wk.cb != cur_cb) {                    // a new column block: its accumulator must be drained
@@ -387,50 +394,53 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
                     cur_cb = wk.cb;
                     accumulate = 0;
                 }
-                mbar_wait(full_bar(stage.i), stage.phase, a.status);
+                mbar_wait(x_full(xr.i), xr.phase, a.status);
                 mbar_wait(a_full(ar.i), ar.phase, a.status);
                 tc_fence_after();
-                const uint32_t xbase = smem_u32(stage0 + stage.i * C::STAGE_BYTES);
+                const uint32_t xbase = smem_u32(xring + xr.i * C::X_BYTES);
                 const uint32_t abase = tmem + ar.i * (KTS * 32);
                 const uint32_t d = tmem + C::D_COL0 + dr.i * NB;
-                if (tr != nullptr && wk.it == begin && wk.sub == 0) tc_stamp(tr, 5);
+                if (tr != nullptr && leader && wk.it == begin && wk.sub == 0) tc_stamp(tr, 5);
 #pragma unroll
                 for (int kt = 0; kt < KTS; ++kt) {
                     if (kt < nkt) {
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
-                            tc_mma_ts(d, abase + kt * 32 + ks * 8, smem_desc(xbase + kt * C::XTILE + ks * 32), idesc, accumulate);
+                            const uint64_t bdesc = smem_desc(xbase + kt * C::XTILE + ks * 32);
+                            if (leader) tc_mma_ts(d, abase + kt * 32 + ks * 8, bdesc, idesc, accumulate);
                             accumulate = 1;
                         }
                     }
                 }
-                tc_commit(empty_bar(stage.i));            // arrive when the tensor core has read the stage's activations
-                tc_commit(a_empty(ar.i));                 // ... and its dequantised weights
-                tc_stamp(tr, 7);
+                if (leader) {
+                    tc_commit(x_empty(xr.i));             // arrive when the tensor core has read the stage's activations
+                    tc_commit(a_empty(ar.i));             // ... and its dequantised weights
+                    tc_stamp(tr, 7);
+                }
                 wk.advance();
                 if (!wk.valid() || wk.cb != cur_cb) {     // the segment's last stage: its sums are complete after these
-                    tc_commit(d_full(dr.i));
+                    if (leader) tc_commit(d_full(dr.i));
                     dr.next();
                 }
                 ar.next();
-                stage.next();
+                xr.next();
+                __syncwarp();
             }
         }
-        __syncwarp();            // the warp reaches the closing barrier (and the tensor-memory release) together
     } else if (warp < kDequant) {
         // ------------------- dequantisers: 4-bit codes -> bf16(s * q + b) -> tensor memory (A operand) ---------
         const int q = warp & 3, part = warp >> 2;         // TMEM lane quarter; which k-step (16 inputs) of a k tile
         const int hf = part >> 1;
-        Ring stage(STAGES, 0), ar(AU, 1);
+        Ring wr(WS, 0), ar(AU, 1);
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
         uint32_t nib_mask = 0x000F000Fu, magic = 0x43004300u;      // bf16 128 + code
         asm volatile("" : "+r"(nib_mask), "+r"(magic));
         const __nv_bfloat162 c128 = __floats2bfloat162_rn(128.f, 128.f);
         for (StageWalk<KTS> wk(begin, end, SPB, KT); wk.valid(); wk.advance()) {
             const int nkt = wk.nkt();
-            mbar_wait(full_bar(stage.i), stage.phase, a.status);
+            mbar_wait(w_full(wr.i), wr.phase, a.status);
             if (tr != nullptr && threadIdx.x == 0 && wk.it == begin && wk.sub == 0) tc_stamp(tr, 3);
-            const uint8_t* wst = stage0 + stage.i * C::STAGE_BYTES + C::X_BYTES;
+            const uint8_t* wst = wring + wr.i * C::W_BYTES;
             uint2 u[KTS];
             uint32_t sbw[KTS];
             // the group of this k-step's inputs: the tile's only one, or (32-input groups) group hf
@@ -472,10 +482,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
             if (tr != nullptr && threadIdx.x == 0 && wk.it == begin && wk.sub == 0) tc_stamp(tr, 13);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(a_full(ar.i)); mbar_arrive(empty_bar(stage.i)); }
+            if (lane == 0) { mbar_arrive(a_full(ar.i)); mbar_arrive(w_empty(wr.i)); }
             if (tr != nullptr && threadIdx.x == 0) { if (wk.it == begin && wk.sub == 0) tc_stamp(tr, 4); tc_stamp(tr, 6); }
             ar.next();
-            stage.next();
+            wr.next();
         }
     } else {
         // ------------------- epilogue warps: a column block's sums from tensor memory -> output ----------
@@ -499,7 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
             const int col = cb * kCols + col_local;
             // slot 2*cta + 1 when this CTA entered the column block from an earlier one, else 2*cta
             float* slot = slots + (size_t)(2 * blockIdx.x + (begin < cb_begin ? 1 : 0)) * kSlotFloats;
-            mbar_wait(d_full(dr.i), dr.phase, a.status);
+            mbar_wait_idle(d_full(dr.i), dr.phase, a.status);
             if (tr != nullptr && warp == kDequant + 2 && lane == 0 && seg_begin == begin) tc_stamp(tr, 8);
             tc_fence_after();
 #pragma unroll 1
@@ -543,13 +553,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
             if (!whole) finish_segment(a, cb, SPB, total, col_local, seg_list);
             if (warp == kDequant + 2 && lane == 0) tc_stamp(tr, 9);
         }
-        if (warp == kDequant + 2 && lane == 0) epi_finished = 1;
     }
 
     // ---- everyone is done with the tensor memory: give it back ----
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) { tc_stamp(tr, 10); if (tr != nullptr && epi_finished == 0) tr[blockIdx.x * 16 + 10] = 0; }
+    if (threadIdx.x == 0) tc_stamp(tr, 10);
     if (warp == kDequant + 1) {
         tc_fence_after();
         const uint32_t ncols = C::TMEM_COLS;
@@ -557,11 +566,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_kernel(const __grid_constant_
     }
 }
 
-template <int G, int NB, int KTS, int STAGES>
+template <int G, int NB, int KTS, int XS>
 int launch(const Args& a, cudaStream_t stream) {
-    using C = Cfg<G, NB, KTS, STAGES>;
-    static_assert(C::SMEM <= 227 * 1024, "stage ring does not fit shared memory");
-    auto kern = qmm_kernel<G, NB, KTS, STAGES>;
+    using C = Cfg<G, NB, KTS, XS>;
+    static_assert(C::SMEM <= 227 * 1024, "the rings do not fit shared memory");
+    auto kern = qmm_kernel<G, NB, KTS, XS>;
     // the opt-in is per device: keep one flag per device ordinal
     static bool configured[64] = {};
     int dev = 0;
@@ -585,21 +594,12 @@ int launch(const Args& a, cudaStream_t stream) {
     return TF_OK;
 }
 
-// as many stages as fit ~210 KB of shared memory (at most 8): the ring has to cover the copy latency
-// plus the stages the dequantisers and the tensor core hold at any moment
-template <int G, int NB, int KTS>
-constexpr int stages_for() {
-    constexpr int stage = ((KTS * rec_bytes(G) + KTS * NB * 128 + 1023) / 1024) * 1024;
-    constexpr int n = (210 * 1024) / stage;
-    return n > 8 ? 8 : n;
-}
-
 template <int G>
 int dispatch(const Args& a, cudaStream_t stream) {
-    // <group, row bucket, k tiles per stage, stages>
-    if (a.M <= 32) return launch<G, 32, 4, stages_for<G, 32, 4>()>(a, stream);
-    if (a.M <= 64) return launch<G, 64, 2, stages_for<G, 64, 2>()>(a, stream);
-    return launch<G, 128, 4, stages_for<G, 128, 4>()>(a, stream);
+    // <group, row bucket, k tiles per stage, activation stages>: 64 KB of activations a stage at 128 rows
+    if (a.M <= 32) return launch<G, 32, 4, 4>(a, stream);
+    if (a.M <= 64) return launch<G, 64, 4, 4>(a, stream);
+    return launch<G, 128, 4, 2>(a, stream);
 }
 
 // ---- relayout kernels: one thread per output word / pair -----------------------------------------
