@@ -700,7 +700,7 @@ def main():
 
     # ---- extra: the same forward over 16 concurrent sequences x W rows (context set directly) ----
     batch16 = None
-    if not args.no_batch16 and args.seqs == 1 and 16 * args.width <= 128:
+    if not args.no_batch16 and world == 1 and args.seqs == 1 and 16 * args.width <= 128:
         F.enable_wide(w)                 # 128 rows a step: the tcgen05 wide-row kernel for every matmul of this state
         st16 = F.State(w, 16, args.ctx + 2 * args.width, dev, wide=True)
         run16 = runner.LaneRunner(w, st16, [args.width] * 16, max_context=args.ctx + args.width, tp=tp)
