@@ -317,6 +317,64 @@ def only_qmm(args, dev):
                       "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "peak_kind": kind}))
 
 
+def only_timeline(args, dev):
+    """Where a verify step's time goes around its matmuls: one captured step of --layers layers (1 sequence x
+    --width rows, context set directly) with the lane matmul's timeline hook on (`tf_qmm_set_trace`: globaltimer
+    stamps per CTA and launch). Per kind of projection, medians over the layers after the first: the time from the
+    predecessor's memory being visible to the first stage in shared memory, the main loop, the K-segment finish and
+    output (tail), and the gap until the next matmul may start (the glue kernels between them)."""
+
+    import numpy as np
+    import torch
+
+    from tensorfold_b200 import _lib, forward as F, runner, synthetic
+
+    cfg = F.Config(**dict(synthetic.DENSE_27B, layers=args.layers))
+    w = synthetic.random_weights(cfg, seed=2, device=dev)
+    st = F.State(w, 1, args.ctx + 2 * args.width, dev)
+    run = runner.LaneRunner(w, st, [args.width], max_context=args.ctx + args.width)
+    run.capture()
+    st.lens = [args.ctx]
+    run.refresh()
+    run.tokens.copy_(torch.randint(0, cfg.vocab, (args.width,), device=dev, dtype=torch.int32))
+    for _ in range(10):
+        run.step_device()
+    torch.cuda.synchronize(dev)
+    slots, launches, workers = 16, 512, 148
+    tr = torch.zeros(workers + launches * workers * slots, dtype=torch.int64, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.tf_qmm_set_trace(tr.data_ptr()), "set_trace")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run.step_device()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    lib.tf_qmm_set_trace(None)
+    n = 4 * args.layers + 1
+    t = tr.cpu().numpy()[workers:].reshape(launches, workers, slots).astype(np.float64)
+
+    def stat(launch, slot, f=np.median):
+        col = t[launch, :, slot]
+        col = col[col > 0]
+        return float(f(col)) if len(col) else float("nan")
+    kinds = ["in_proj", "out_proj", "gate_up", "down"]
+    rows = {k: [] for k in kinds}
+    for i in range(4, n - 1):                       # skip the first layer (cold) and the head
+        wait, first, loop = stat(i, 2), stat(i, 3), stat(i, 4)
+        ends = [v for v in (stat(i, 9, np.max), stat(i, 6, np.max)) if v == v]
+        end = max(ends)
+        rows[kinds[i % 4]].append((first - wait, loop - first, end - loop, stat(i + 1, 2) - end))
+    out = {"only": "timeline", "layers": args.layers, "step_us_with_tracing": 1000.0 * e0.elapsed_time(e1), "unit": "us (medians)"}
+    busy = gaps = 0.0
+    for k in kinds:
+        a = np.median(np.array(rows[k]), axis=0) / 1000.0
+        out[k] = {"fill": round(a[0], 2), "main_loop": round(a[1], 2), "tail": round(a[2], 2), "gap_to_next_matmul": round(a[3], 2)}
+        busy += a[0] + a[1] + a[2]
+        gaps += a[3]
+    out["per_layer"] = {"matmul_busy": round(busy, 2), "between_matmuls": round(gaps, 2)}
+    print(json.dumps(out))
+
+
 def only_gdn(args, dev):
     """The gated-DeltaNet lane step alone (conv1d + gates + recurrence + gated norm, one fused kernel per layer):
     --seqs sequences x --width rows, 16 QK heads, 32 V heads, head dim 128, fp32 state N(0, 0.1) per layer;
@@ -567,7 +625,7 @@ def main():
                     "mixture-of-experts hybrid (group 32, 128 experts top-8 + shared) on a ragged batch of 32 sequences")
     ap.add_argument("--only", default="", help="'qmm': time the lane matmul alone on --shape with --rows rows and exit; "
                     "'prefill': the same for the tcgen05 prefill-width matmul; 'gdn': the gated-DeltaNet lane step alone on --seqs x --width rows; "
-                    "'attn': lane attention alone on --seqs x --width rows at --ctx")
+                    "'attn': lane attention alone on --seqs x --width rows at --ctx; 'timeline': per-role breakdown of the matmuls of a step")
     ap.add_argument("--shape", default="17408x5120")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=4, help="--only qmm: weight copies rotated through (4 x 50 MB > L2)")
@@ -625,6 +683,8 @@ def main():
 
     if args.only in ("qmm", "prefill"):
         return only_qmm(args, dev)
+    if args.only == "timeline":
+        return only_timeline(args, dev)
     if args.only == "gdn":
         return only_gdn(args, dev)
     if args.only == "attn":
