@@ -149,3 +149,22 @@ def test_wrong_arguments_raise(qmm):
         qmm.lane_matmul(x, q)                      # CPU tensor: there is no CPU path
     with pytest.raises(ValueError):
         qmm.tile_weight(words.cuda(), scales.cuda().float(), biases.cuda())
+
+
+def test_head_shape_248320_by_5120(qmm):
+    """The vocabulary head of the 27B-class model (the largest matmul of a step, 715 MB of weights): a row alone has
+    the bits of the row in an 8-row window, and 4096 sampled output columns agree with the oracle."""
+
+    n, k, group, rows = 248320, 5120, 64, 8
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    words = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, dtype=torch.int64, device="cuda").to(torch.int32)
+    scales = ((torch.rand((n, k // group), generator=gen, device="cuda") / 8 + 1 / 64) * (4.0 / k ** 0.5)).to(torch.bfloat16)
+    biases = (-7.5 * scales.float()).to(torch.bfloat16)
+    x = torch.randn((rows, k), generator=gen, device="cuda").to(torch.bfloat16)
+    q = qmm.tile_weight(words, scales, biases, group)
+    full = qmm.lane_matmul(x, q)
+    for r in (0, 3, 7):
+        assert_same_bits(qmm.lane_matmul(x[r:r + 1], q), full[r:r + 1], f"head: row {r} alone")
+    cols = torch.randperm(n, generator=torch.Generator().manual_seed(5))[:4096].sort().values
+    want = O.qmm(x.cpu(), words[cols.cuda()].cpu(), scales[cols.cuda()].cpu(), biases[cols.cuda()].cpu(), group)
+    assert_close(full[:, cols.cuda()], want, "head columns vs oracle")
