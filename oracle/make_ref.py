@@ -3,7 +3,7 @@
 Test infrastructure only: the files it produces live under ``oracle/_ref/`` (git-ignored, never
 committed, never imported by the package) and are read by ``tests/test_reference_gpu.py`` and by the
 optional ``reference_gpu`` leg of ``bench.py``. It copies, unmodified, the few source files of the
-reference's Triton/CUDA lane path from a checkout of the reference (default ``/root/reference``) into a
+reference's Triton/CUDA lane path from a checkout of the reference (the path given, or the default below) into a
 package skeleton, so that ``import tensorfold.families.qwen3_5.cuda.qmm`` works where the checkout does
 not exist. Nothing is built here: the Triton kernels compile on first use and the gdn kernels
 (``gdn_tree.cu`` / ``gdn.cu``) are JIT-built by the reference's own loader.
