@@ -165,6 +165,11 @@ int tf_norm_xs(const void* x, const void* residual, const void* partials, int np
  * Replaces: families/qwen3_5/cuda/glue.py:133-154 (swiglu), lane_glue.py:307-317 (mlp_act). */
 int tf_swiglu(const void* gate, const void* up, size_t in_stride, void* out_packed, void* out_rows, int M, int I,
               int group, void* stream);
+/* The same for a [gate; up] stack whose output columns are interleaved by 16-column tile (tile 2a = gate columns
+ * 16a..16a+15, tile 2a+1 = up columns 16a..16a+15): gate_up [M, >= 2 I] with row stride in_stride. This is the
+ * order tf_qmm_act wants the stacked weight in; both give the same bits. No reference counterpart for the order. */
+int tf_swiglu_tiled(const void* gate_up, size_t in_stride, void* out_packed, void* out_rows, int M, int I, int group,
+                    void* stream);
 
 /* out = bf16(silu(z) * (y * rsqrt(mean_head(y^2) + eps) * weight)) per value head; y [M, v_heads, dv]
  * contiguous, z a [M, v_heads*dv] view with row stride z_stride, dv = 128.
@@ -387,6 +392,13 @@ int tf_peer_exchange(const float* local, int rows, int D, void* const* peer_bufs
  * tf_peer_slot_bytes(rows, D, world), zero before first use; seq and tickets: one zeroed 32-bit word each.
  * Replaces: families/qwen3_5/cuda/distributed.py:267-289 (row_partial + gather_rank_partials +
  * sum_rank_partials) around the two row-parallel projections of a layer. */
+/* tf_qmm_next for the stacked [gate; up] projection (columns interleaved by 16-column tile, see tf_swiglu_tiled) with
+ * the SwiGLU fused into the epilogue: no y; the owner of each column block writes bf16(silu(bf16 gate) * bf16 up) and
+ * its group sums as the packed input (N / 2 inputs, group `group`) of the down projection - the bits tf_swiglu_tiled
+ * writes from the same projection's output. M is 1..8 (the bucket whose warps own a gate tile and its up tile).
+ * Replaces: glue.swiglu after the gate and up matmuls (families/qwen3_5/cuda/forward.py:186-189). */
+int tf_qmm_act(const void* x_packed, const void* w_tiled, void* act_packed, void* scratch, size_t scratch_bytes, int M, int N,
+               int K, int group, const void* next_w_tiled, int next_N, int next_K, int next_group, int* status, void* stream);
 int tf_qmm_peer(const void* x_packed, const void* w_tiled, void* scratch, size_t scratch_bytes, int M, int N, int K, int group,
                 void* const* peer_bufs, size_t slot_bytes, const void* seq, int rank, int world, const void* next_w_tiled,
                 int next_N, int next_K, int next_group, int* status, void* stream);

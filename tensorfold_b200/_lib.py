@@ -96,6 +96,9 @@ SIGNATURES: dict[str, tuple] = {
     "tf_peer_slot_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tf_peer_exchange": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_void_p]),
+    "tf_qmm_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                           c_int, c_void_p, c_void_p]),
+    "tf_swiglu_tiled": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tf_qmm_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p,
                             c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "tf_norm_xs_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

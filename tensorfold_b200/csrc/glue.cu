@@ -150,9 +150,12 @@ __global__ void norm_xs_kernel(const __nv_bfloat16* x, const __nv_bfloat16* r, c
 }
 
 // ---- swiglu: rows x (I/8) threads -----------------------------------------------------------------
+// `tiled`: gate and up come interleaved by 16-column tile in one row ([gate 16a..16a+15 | up 16a..16a+15] for
+// activation tile a), the order in which the lane matmul's SwiGLU epilogue wants the stacked weight; `gate` is then
+// the row's start and `up` is unused.
 template <int G>
 __global__ void swiglu_kernel(const __nv_bfloat16* gate, const __nv_bfloat16* up, size_t in_stride, uint8_t* out_packed,
-                              __nv_bfloat16* out_rows, int M, int I) {
+                              __nv_bfloat16* out_rows, int M, int I, int tiled) {
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.y;
@@ -161,8 +164,10 @@ __global__ void swiglu_kernel(const __nv_bfloat16* gate, const __nv_bfloat16* up
     const bool live = c < (I >> 3) && row < M;
     if (live) {
         float g[8], u[8], o[8];
-        unpack8(*reinterpret_cast<const uint4*>(gate + (size_t)row * in_stride + 8 * c), g);
-        unpack8(*reinterpret_cast<const uint4*>(up + (size_t)row * in_stride + 8 * c), u);
+        const size_t goff = tiled ? (size_t)(c >> 1) * 32 + (c & 1) * 8 : (size_t)8 * c;
+        const __nv_bfloat16* urow = tiled ? gate + 16 : up;
+        unpack8(*reinterpret_cast<const uint4*>(gate + (size_t)row * in_stride + goff), g);
+        unpack8(*reinterpret_cast<const uint4*>(urow + (size_t)row * in_stride + goff), u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = g[i] * sigmoidf_(g[i]) * u[i];
         ov = pack8(o);
@@ -405,7 +410,20 @@ int tf_swiglu(const void* gate, const void* up, size_t in_stride, void* out_pack
     if (!gate || !up || !out_packed || in_stride % 8) return TF_EINVAL;
     if (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out_packed | (uintptr_t)out_rows) & 15) return TF_EALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    void* args[] = {&gate, &up, &in_stride, &out_packed, &out_rows, &M, &I};
+    int tiled = 0;
+    void* args[] = {&gate, &up, &in_stride, &out_packed, &out_rows, &M, &I, &tiled};
+    const void* fn = group == 64 ? (const void*)tf::swiglu_kernel<64> : (const void*)tf::swiglu_kernel<32>;
+    return tf::finish(tf::launch_pdl(fn, dim3((I / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args, 3));
+}
+
+int tf_swiglu_tiled(const void* gate_up, size_t in_stride, void* out_packed, void* out_rows, int M, int I, int group, void* stream) {
+    if (M < 1 || M > TF_QMM_MAX_ROWS || I < 64 || I % 64 || (group != 64 && group != 32)) return TF_EINVAL;
+    if (!gate_up || !out_packed || in_stride % 8 || in_stride < (size_t)2 * I) return TF_EINVAL;
+    if (((uintptr_t)gate_up | (uintptr_t)out_packed | (uintptr_t)out_rows) & 15) return TF_EALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int tiled = 1;
+    const void* up = nullptr;
+    void* args[] = {&gate_up, &up, &in_stride, &out_packed, &out_rows, &M, &I, &tiled};
     const void* fn = group == 64 ? (const void*)tf::swiglu_kernel<64> : (const void*)tf::swiglu_kernel<32>;
     return tf::finish(tf::launch_pdl(fn, dim3((I / 8 + 255) / 256, tf::tf_padded_rows(M)), dim3(256), 0, st, args, 3));
 }

@@ -120,6 +120,11 @@ struct Args {
     const uint32_t* peer_seq;
     size_t peer_slot_bytes;
     int peer_rank, peer_world;
+    // SwiGLU epilogue (may be null): the weight is a [gate; up] stack interleaved by column tile (tile 2a = gate
+    // columns 16a..16a+15, tile 2a+1 = up columns 16a..16a+15), a consumer warp owns both tiles of an activation tile,
+    // and instead of y the block's owner writes bf16(silu(bf16 gate) * bf16 up) with its group sums as the packed
+    // input of the down projection (N / 2 inputs) - the bits the separate SwiGLU kernel would write
+    uint8_t* act_packed;
     const int* prob_expert;
     const int* prob_count;
     const int* prob_sel;
@@ -424,6 +429,44 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS) qmm_kernel(const Args a) 
             if (tr != nullptr && threadIdx.x == 0) stamp(tr, 6);
         }
         // a whole block, or a finished one: write the output
+        if constexpr (!MULTI && T == 2) {
+            if (a.act_packed != nullptr) {
+                __shared__ float act_part[kWarps / 2][C::ROWS];
+                const int at = cb * (kWarps / 2) + warp;            // activation tile: 16 inputs of the down projection
+                const int q4 = at & 3;                              // its place in the down projection's k tile
+                uint8_t* tile = a.act_packed + (size_t)(at >> 2) * (C::ROWS * (128 + 4 * C::GPT));
+                const bool in_range = at * 16 < (a.N >> 1);
+#pragma unroll
+                for (int rb = 0; rb < MB; ++rb)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int row = rb * 8 + 2 * t + j;
+                        float pair = 0.f;
+#pragma unroll
+                        for (int hsel = 0; hsel < 2; ++hsel) {
+                            const float gv = round_bf16(acc[0][rb][2 * hsel + j]), uv = round_bf16(acc[1][rb][2 * hsel + j]);
+                            const float ov = round_bf16(gv * sigmoidf_(gv) * uv);
+                            if (in_range)
+                                *reinterpret_cast<__nv_bfloat16*>(tile + row * 128 + (((2 * q4 + hsel) * 16) ^ ((row & 1) << 6)) + g * 2) = f2bf(ov);
+                            // the chunk's eight values added in column order (as the separate kernel's lane does), then the pair of chunks
+                            float cs = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cs += __shfl_sync(0xffffffffu, ov, i * 4 + t);
+                            pair = hsel == 0 ? cs : pair + cs;
+                        }
+                        if (g == 0) act_part[warp][row] = pair;
+                    }
+                named_bar_sync(4, NC);
+                constexpr int WPG = 4 / C::GPT;                     // warps (activation tiles) per group
+                if ((warp % WPG) == 0 && lane < C::ROWS && in_range) {
+                    float sum = act_part[warp][lane] + act_part[warp + 1][lane];
+                    if (WPG == 4) sum = sum + (act_part[warp + 2][lane] + act_part[warp + 3][lane]);
+                    reinterpret_cast<float*>(tile + C::ROWS * 128)[(C::GPT == 1 ? 0 : (q4 >> 1)) * C::ROWS + lane] = sum;
+                }
+                named_bar_sync(4, NC);
+                continue;
+            }
+        }
         if (!MULTI && a.peer_bufs != nullptr) {
             // a tensor-parallel rank's partial: straight into every rank's exchange buffer, self-signalling
             const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(a.peer_seq) + 1u;
@@ -503,6 +546,8 @@ struct PeerOut {
     int rank = 0, world = 0;
 };
 thread_local PeerOut g_peer;
+// the SwiGLU destination of the launch being set up (tf_qmm_act hands it to tf_qmm_next on the same thread)
+thread_local uint8_t* g_act = nullptr;
 
 inline int prefetch_bytes() {
     static const int v = [] { const char* e = std::getenv("TF_QMM_PREFETCH_KB"); return (e ? atoi(e) : 224) * 1024; }();
@@ -642,7 +687,7 @@ int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratc
     if (M < 1 || M > TF_QMM_MAX_ROWS || N < 1 || K < 64 || K % 64) return TF_EINVAL;
     if (group != 64 && group != 32) return TF_EINVAL;
     if (flags & ~TF_QMM_F32_OUT) return TF_EINVAL;
-    if (!x_packed || !w_tiled || (!y && tf::g_peer.bufs == nullptr)) return TF_EINVAL;
+    if (!x_packed || !w_tiled || (!y && tf::g_peer.bufs == nullptr && tf::g_act == nullptr)) return TF_EINVAL;
     const long long CB = (N + tf::kCols - 1) / tf::kCols, IT = tf::item_tiles_for((int)CB, K / 64), SPB = (K / 64 + IT - 1) / IT;
     if (CB * SPB > (1 << 30) / tf::kWorkers) return TF_EINVAL;
     if (((uintptr_t)x_packed | (uintptr_t)w_tiled) & 15) return TF_EALIGN;
@@ -666,8 +711,21 @@ int tf_qmm_next(const void* x_packed, const void* w_tiled, void* y, void* scratc
     a.peer_rank = tf::g_peer.rank; a.peer_world = tf::g_peer.world;
     tf::g_peer = tf::PeerOut();
     if (a.peer_bufs != nullptr) a.y = nullptr;
+    a.act_packed = tf::g_act;
+    tf::g_act = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return group == 64 ? tf::dispatch<64>(a, st) : tf::dispatch<32>(a, st);
+}
+
+int tf_qmm_act(const void* x_packed, const void* w_tiled, void* act_packed, void* scratch, size_t scratch_bytes, int M, int N, int K,
+               int group, const void* next_w_tiled, int next_N, int next_K, int next_group, int* status, void* stream) {
+    // the row bucket whose consumer warps own a gate tile and its up tile; whole activation tiles
+    if (M < 1 || M > 8 || N < 32 || N % 32 || !act_packed || ((uintptr_t)act_packed & 15)) return TF_EINVAL;
+    tf::g_act = static_cast<uint8_t*>(act_packed);
+    const int rc = tf_qmm_next(x_packed, w_tiled, nullptr, scratch, scratch_bytes, M, N, K, group, 0, next_w_tiled, next_N, next_K,
+                               next_group, status, stream);
+    tf::g_act = nullptr;
+    return rc;
 }
 
 int tf_qmm_peer(const void* x_packed, const void* w_tiled, void* scratch, size_t scratch_bytes, int M, int N, int K, int group,
@@ -709,6 +767,7 @@ int tf_qmm_grouped(const void* x_packed, const void* w_tiled, const int* prob_ex
     a.prob_expert = prob_expert; a.prob_count = prob_count; a.prob_sel = prob_sel; a.max_probs = max_probs;
     a.next_w = nullptr; a.next_N = a.next_K = a.next_group = a.prefetch_bytes = 0;
     a.peer_bufs = nullptr; a.peer_seq = nullptr; a.peer_slot_bytes = 0; a.peer_rank = a.peer_world = 0;
+    a.act_packed = nullptr;
     a.w_stride = (long long)tf_qmm_tiled_bytes(N, K, group);
     a.xp_stride = (long long)tf_packed_bytes(8, K, group);
     a.y_stride = 8ll * N;

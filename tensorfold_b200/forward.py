@@ -143,6 +143,20 @@ def _stack(parts, device, group) -> QWeight:
     return tile_weight(words.contiguous(), scales.contiguous(), biases.contiguous(), group)
 
 
+def interleave_gate_up(gate, up):
+    """[gate; up] rows in the order the fused SwiGLU wants: for activation tile a (16 columns) the 16 gate rows, then
+    the 16 up rows. Returns objects with ``words``, ``scales``, ``biases`` for ``_stack``."""
+
+    from types import SimpleNamespace
+
+    def mix(g, u):
+        n = g.shape[0]
+        if n % 16:
+            raise ValueError("the MLP width must be a multiple of 16")
+        return torch.stack([g.reshape(n // 16, 16, -1), u.reshape(n // 16, 16, -1)], dim=1).reshape(2 * n, -1)
+    return SimpleNamespace(words=mix(gate.words, up.words), scales=mix(gate.scales, up.scales), biases=mix(gate.biases, up.biases))
+
+
 def load_weights(model: dict, device="cuda") -> Weights:
     """Build device weights from stored-layout arrays: ``model`` maps names to objects with ``words``,
     ``scales``, ``biases`` (4-bit projections) or to tensors, as ``families/qwen3_5/cuda/weights.py``
@@ -157,7 +171,7 @@ def load_weights(model: dict, device="cuda") -> Weights:
         def dev(name):
             return src[name].to(device).contiguous()
         moe = "router" in src
-        gate_up = None if moe else _stack([src["gate"], src["up"]], device, g)
+        gate_up = None if moe else _stack([interleave_gate_up(src["gate"], src["up"])], device, g)
         down = None if moe else _stack([src["down"]], device, g)
         extra = {}
         if moe:
@@ -354,7 +368,7 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
         kmax = max(q.k for q in (w.head, *(m for l in w.layers for m in (l.in_proj, l.out_proj, l.gate_up, l.down))))
         staging = torch.empty(prefill_qmm.packed_bytes(R, kmax, g), dtype=torch.uint8, device=dev)
 
-        def lane_matmul(x_, weight, *, f32=False, out=None, next_weight=None, peer=None):      # noqa: F811
+        def lane_matmul(x_, weight, *, f32=False, out=None, next_weight=None, peer=None, act_out=None):      # noqa: F811
             return prefill_qmm.prefill_matmul(x_, w.wide[id(weight)], f32=f32, out=out, staging=staging)
     else:
         lane_matmul = _lane_matmul
@@ -409,8 +423,12 @@ def tree_forward(w: Weights, tokens: torch.Tensor, windows, st: State, *, full_l
             pending, parts = lane_moe.moe(hrows, layer.router, layer.experts, moe_buf, ep), None
             continue
         x, h = norm(x, r, layer.post_norm, partials=rparts)
-        gu = lane_matmul(h, layer.gate_up, out=mlp_in, next_weight=layer.down)
-        act = lane_glue.mlp_act(gu[:, :c.intermediate], gu[:, c.intermediate:], group=g)
+        if R <= 8 and not st.wide:
+            # SwiGLU in the gate_up matmul's epilogue (the same bits as the separate kernel below)
+            act = lane_matmul(h, layer.gate_up, act_out=new_packed(R, c.intermediate, g, dev), next_weight=layer.down)
+        else:
+            gu = lane_matmul(h, layer.gate_up, out=mlp_in, next_weight=layer.down)
+            act = lane_glue.mlp_act_tiled(gu, c.intermediate, group=g)
         pending, parts = row_parallel(act, layer.down, after(li))
     if not full_logits:
         _, hrows = norm(x, pending, w.norm, rows_out=True, packed_out=False, partials=parts)

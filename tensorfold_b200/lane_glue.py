@@ -100,6 +100,24 @@ def mlp_act(gate: torch.Tensor, up: torch.Tensor, *, group: int = 64, rows_out: 
 swiglu = mlp_act
 
 
+def mlp_act_tiled(gate_up: torch.Tensor, intermediate: int, *, group: int = 64, rows_out: bool = False,
+                  out: Packed | None = None):
+    """``mlp_act`` for the output (M, >= 2 I) of a stacked [gate; up] projection whose columns are interleaved by
+    16-column tile (``forward.interleave_gate_up``): the same bits as ``mlp_act`` on the separate halves."""
+
+    _bf16(gate_up)
+    m = gate_up.shape[0]
+    _rows(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] < 2 * intermediate or gate_up.stride(1) != 1:
+        raise ValueError("mlp_act_tiled: gate_up must be (M, >= 2 I) rows")
+    packed = out if out is not None else new_packed(m, intermediate, group, gate_up.device)
+    rows = torch.empty((m, intermediate), dtype=torch.bfloat16, device=gate_up.device) if rows_out else None
+    with torch.cuda.device(gate_up.device):
+        _lib.check(_lib.load().tf_swiglu_tiled(gate_up.data_ptr(), gate_up.stride(0), packed.data.data_ptr(), _lib.ptr(rows), m,
+                                               intermediate, group, _lib.stream()), "mlp_act_tiled")
+    return (packed, rows) if rows_out else packed
+
+
 def gdn_post(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, *, group: int = 64,
              rows_out: bool = False, out: Packed | None = None):
     """SiLU(z) * RMSNorm(y) * weight per value head: y (M, nv, dv), z (M, nv*dv) -> packed (M, nv*dv).
@@ -215,4 +233,4 @@ def embed(ids: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor, biases:
     return out
 
 
-__all__ = ["attn_prep", "embed", "gate_mul", "gated_norm", "gdn_post", "gdn_pre", "mlp_act", "norm_xs", "swiglu"]
+__all__ = ["attn_prep", "embed", "gate_mul", "gated_norm", "gdn_post", "gdn_pre", "mlp_act", "mlp_act_tiled", "norm_xs", "swiglu"]

@@ -203,7 +203,8 @@ def _as_qweight(weight, scales, biases) -> QWeight:
 
 def lane_matmul(x: torch.Tensor | Packed, weight, scales: torch.Tensor | None = None, biases: torch.Tensor | None = None, *,
                 xs: torch.Tensor | None = None, sk: int | None = None, f32: bool = False,
-                out: torch.Tensor | None = None, next_weight: QWeight | None = None, peer=None) -> torch.Tensor:
+                out: torch.Tensor | None = None, next_weight: QWeight | None = None, peer=None,
+                act_out: Packed | None = None) -> torch.Tensor:
     """x (..., K) bf16 — or rows already ``Packed`` by the producing kernel — times the 4-bit
     ``weight`` (N, K) transposed -> (..., N) bf16.
 
@@ -216,7 +217,10 @@ def lane_matmul(x: torch.Tensor | Packed, weight, scales: torch.Tensor | None = 
     ``next_weight``: the weight of the matmul launched next on this stream; its first bytes are pulled
     into L2 while this one finishes (a hint only). ``peer``: a ``distributed.RankGroup`` with the fused
     exchange: the fp32 sums go straight into every rank's exchange buffer (nothing is returned; the next
-    ``norm_xs(..., peer=...)`` adds the ranks' partials).
+    ``norm_xs(..., peer=...)`` adds the ranks' partials). ``act_out``: for a stacked [gate; up] weight with columns
+    interleaved by 16-column tile and at most 8 rows: the SwiGLU runs in the matmul's epilogue and its packed result
+    (the down projection's input, N / 2 wide) is written to ``act_out``, which is returned - the bits
+    ``lane_glue.mlp_act_tiled`` gives on the projection's output.
     """
 
     lib = _lib.load()
@@ -258,6 +262,18 @@ def lane_matmul(x: torch.Tensor | Packed, weight, scales: torch.Tensor | None = 
                                        nw.k if nw is not None else 0, nw.group if nw is not None else 0,
                                        _lib.status(dev).word.data_ptr(), _lib.stream()), "lane_matmul (peer)")
         return None
+    if act_out is not None:
+        if len(chunks) != 1 or m > 8 or weight.n % 32 or act_out.m != m or act_out.k != weight.n // 2 or act_out.group != weight.group:
+            raise ValueError("lane_matmul: act_out needs at most 8 rows and a packed buffer of N / 2 inputs")
+        nw = next_weight
+        with torch.cuda.device(dev):
+            scratch = scratch_for(dev)
+            _lib.check(lib.tf_qmm_act(chunks[0].data.data_ptr(), weight.tiled.data_ptr(), act_out.data.data_ptr(), scratch.data_ptr(),
+                                      scratch.numel(), m, weight.n, weight.k, weight.group,
+                                      nw.tiled.data_ptr() if nw is not None else None, nw.n if nw is not None else 0,
+                                      nw.k if nw is not None else 0, nw.group if nw is not None else 0,
+                                      _lib.status(dev).word.data_ptr(), _lib.stream()), "lane_matmul (act)")
+        return act_out
     dtype = torch.float32 if f32 else torch.bfloat16
     if out is None:
         out = torch.empty((m, weight.n), dtype=dtype, device=dev)

@@ -228,3 +228,34 @@ def test_lane_fuse_stacks_and_reads_in_place(mods):
     assert torch.equal(a.data, b.data)
     lane_fuse.clear(model)
     assert lane_fuse.gdn_in(layer, x) is None
+
+
+@pytest.mark.parametrize("group", [64, 32])
+@pytest.mark.parametrize("rows", [1, 5, 8])
+def test_swiglu_in_the_matmul_epilogue_has_the_bits_of_the_separate_kernel(mods, group, rows):
+    """[gate; up] interleaved by 16-column tile: the lane matmul's SwiGLU epilogue writes the packed input of the down
+    projection with the bits of matmul -> ``mlp_act_tiled``, which in turn equals ``mlp_act`` on the separated halves."""
+
+    from tensorfold_b200 import forward as F
+
+    glue, qmm = mods
+    inter, k = 1280, 1024                       # 2 I = 2560 output columns = ten column blocks: K is cut, blocks have owners
+    gen = torch.Generator().manual_seed(91 + rows)
+    gate, up = O.random_q4(gen, inter, k, group), O.random_q4(gen, inter, k, group)
+    mixed = F.interleave_gate_up(gate, up)
+    w = qmm.tile_weight(mixed.words.cuda(), mixed.scales.cuda(), mixed.biases.cuda(), group)
+    x = torch.randn((rows, k), generator=gen).to(BF).cuda()
+    xp = qmm.pack_rows(x, group)
+    gu = qmm.lane_matmul(xp, w)
+    separate = glue.mlp_act_tiled(gu, inter, group=group)
+    fused = qmm.lane_matmul(xp, w, act_out=qmm.new_packed(rows, inter, group, "cuda"))
+    torch.cuda.synchronize()
+    assert torch.equal(fused.data.cpu(), separate.data.cpu()), "fused SwiGLU epilogue differs from the separate kernel"
+    tiles = gu.reshape(rows, inter // 16, 2, 16)
+    halves = torch.cat([tiles[:, :, 0].reshape(rows, inter), tiles[:, :, 1].reshape(rows, inter)], dim=1).contiguous()
+    plain = glue.mlp_act(halves[:, :inter], halves[:, inter:], group=group)
+    assert torch.equal(plain.data.cpu(), separate.data.cpu()), "mlp_act_tiled differs from mlp_act on the separated halves"
+    # and against the oracle's arithmetic
+    want = O.swiglu(halves[:, :inter].cpu(), halves[:, inter:].cpu())
+    _, got_rows = glue.mlp_act_tiled(gu, inter, group=group, rows_out=True)
+    assert_close(got_rows, want, "tiled SwiGLU vs oracle")
