@@ -313,3 +313,27 @@ def test_presence_cells_keep_a_fast_rank_from_overwriting_a_slot_in_use():
         assert _simulate_expert_exchange(4, 40, True, seed) is None
     # the model does find the overwrite when only data packets couple the ranks
     assert any(_simulate_expert_exchange(4, 40, False, seed) is not None for seed in range(200))
+
+
+def test_gate_up_interleave_is_a_permutation_by_column_tile():
+    """The stacked [gate; up] order of the fused SwiGLU: tile 2a holds gate rows 16a..16a+15, tile 2a+1 the up rows."""
+
+    from types import SimpleNamespace
+
+    from tensorfold_b200.forward import interleave_gate_up
+
+    n, kw = 64, 4
+    mk = lambda base: SimpleNamespace(words=(base + torch.arange(n * kw)).reshape(n, kw).to(torch.int32),
+                                      scales=(base + torch.arange(n * 2)).reshape(n, 2).float(),
+                                      biases=(base - torch.arange(n * 2)).reshape(n, 2).float())
+    gate, up = mk(0), mk(100000)
+    mixed = interleave_gate_up(gate, up)
+    assert mixed.words.shape == (2 * n, kw)
+    for a in range(n // 16):
+        assert torch.equal(mixed.words[32 * a:32 * a + 16], gate.words[16 * a:16 * a + 16])
+        assert torch.equal(mixed.words[32 * a + 16:32 * a + 32], up.words[16 * a:16 * a + 16])
+        assert torch.equal(mixed.scales[32 * a + 16:32 * a + 32], up.scales[16 * a:16 * a + 16])
+        assert torch.equal(mixed.biases[32 * a:32 * a + 16], gate.biases[16 * a:16 * a + 16])
+    with pytest.raises(ValueError):
+        interleave_gate_up(SimpleNamespace(words=torch.zeros((24, 4)), scales=torch.zeros((24, 2)), biases=torch.zeros((24, 2))),
+                           SimpleNamespace(words=torch.zeros((24, 4)), scales=torch.zeros((24, 2)), biases=torch.zeros((24, 2))))
