@@ -560,7 +560,7 @@ int dispatch(const Args& a, cudaStream_t stream) {
     // loads; the wider buckets are bound by the tensor pipe and keep one tile a warp (their accumulators
     // take the registers)
     if (a.M <= 8) return launch<Cfg<G, 1, 4, 2, 1>>(a, stream);
-    if (a.M <= 16) return launch<Cfg<G, 2, 4, 1, 1>>(a, stream);
+    if (a.M <= 16) return launch<Cfg<G, 2, 4, 2, 1>>(a, stream);
     if (a.M <= 32) return launch<Cfg<G, 4, 4, 1, 1>>(a, stream);
     if (a.M <= 64) return launch<Cfg<G, 8, 2, 1, 1>>(a, stream);
     return launch<Cfg<G, 16, 2, 1, 1>>(a, stream);
